@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Benchmark of the BCQ LUT matvec hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1 GPU): the metric configuration, one m = 1 matvec y = x.W with N = K = 12288, q = 3 bit
+planes, group size 128, random BCQ weights.  One "step" is one matvec on each of ROT distinct weight
+sets (ROT x 63.75 MB > 4x the 126 MB L2, so every matvec streams its weights from HBM).
+`value` is effective GB/s = algorithmic bytes / device time with everything resident in HBM;
+`e2e` is the same through the host-buffer C-ABI call (H2D of x and D2H of y inside the timed region).
+With N > 1 ranks every rank runs the same workload on its own weight sets (independent layers, no
+collective on the data path: weak scaling); time is the max over ranks.
+
+`--impl reference` times the reference's CPU path for the same matvec on the host cores:
+lutGEMM::dequantize_cpu (compiled from the reference sources into oracle/_ref, run on k-slabs by
+every host thread) followed by the test's serial fp32 matmul loop (restated in oracle/, OpenMP over
+columns); one matvec per step.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from lutgemm_b200 import synth  # noqa: E402
+
+METRIC = "bcq_gemv_effective_bandwidth"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_lut_kernel launch at the bench shape,
+# from the ncu capture summarised in profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n", type=int, default=12288)
+    ap.add_argument("--k", type=int, default=12288)
+    ap.add_argument("--q", type=int, default=3)
+    ap.add_argument("--g", type=int, default=128)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--rot", type=int, default=8, help="distinct weight sets cycled per step")
+    ap.add_argument("--ntile", type=int, default=0, help="columns per CTA of the matvec (0 = automatic)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return f"bcq_gemv m=1 n={a.n} k={a.k} q={a.q} g={a.g}" + (" +q_bias" if a.bias else "")
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_gemv(a, threads):
+    """One matvec of the workload through the reference's CPU path; returns (seconds, kind, y)."""
+    from oracle import oracle
+    bW, alpha, qb = synth.bcq_layer(a.n, a.k, a.q, a.g, seed=synth.seed_for("bench", a.n, a.k, a.q, 0), with_bias=a.bias)
+    x = synth.activations(1, a.k, seed=123)
+    a_h = alpha.astype(np.float16)
+    oracle.set_threads(threads)
+    have_ref = oracle.ref_cpu() is not None
+    W = np.empty((a.k, a.n), np.float16)
+    t0 = time.perf_counter()
+    if have_ref:
+        # the reference function, unmodified, on disjoint k-slabs (whole groups) from every host thread
+        groups = a.k // a.g
+        per = (groups + threads - 1) // threads
+        def slab(i):
+            g0, g1 = i * per, min(groups, (i + 1) * per)
+            if g0 >= g1:
+                return
+            k0, k1 = g0 * a.g, g1 * a.g
+            W[k0:k1] = oracle.dequantize_cpu(bW[k0 // 32:k1 // 32], a_h[g0:g1], a.g, use_reference=True)
+        ts = [threading.Thread(target=slab, args=(i,)) for i in range(threads)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+    else:
+        W[:] = oracle.dequantize_cpu(bW, a_h, a.g)
+    Wf = W.astype(np.float32)
+    y = oracle.matmul_cpu(x.astype(np.float32), Wf)
+    if qb is not None:
+        y = y + x.astype(np.float32).reshape(1, -1, a.g).sum(-1) @ qb
+    dt = time.perf_counter() - t0
+    return dt, ("reference" if have_ref else "port"), y
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)
+    steps, warm = max(1, min(a.steps, 5)), min(a.warmup, 1)
+    for _ in range(warm):
+        cpu_reference_gemv(a, threads)
+    times = []
+    kind = "port"
+    for _ in range(steps):
+        dt, kind, _ = cpu_reference_gemv(a, threads)
+        times.append(dt)
+    t = sum(times) / len(times)
+    val = B / t / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": steps,
+            "warmup": warm, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(a), "matvecs_per_step": 1},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind,
+                             "sample": "one full matvec per step: dequantize_cpu on k-slabs + serial-k fp32 matmul"},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(a):
+    import torch
+    import lutgemm_b200 as L
+    from lutgemm_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    lib = capi.lib()
+    if a.ntile:
+        lib.lutgemm_set_gemv_ntile(a.ntile)
+
+    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)
+    rot = max(1, a.rot)
+    weights = []
+    for i in range(rot):
+        bW, alpha, qb = synth.bcq_layer(a.n, a.k, a.q, a.g, seed=synth.seed_for("bench", a.n, a.k, a.q, i + 1000 * rank),
+                                        with_bias=a.bias)
+        weights.append(L.nQWeight_fp16(bW, alpha, a.k, a.n, a.q, False, a.k // a.g, qb))
+    x_host = synth.activations(1, a.k, seed=123)
+    x = torch.from_numpy(x_host.view(np.int16)).cuda().view(torch.float16)
+    ys = [torch.empty((1, a.n), dtype=torch.float16, device="cuda") for _ in range(rot)]
+
+    def step():
+        for w, y in zip(weights, ys):
+            L.matmul(y, x, w, 1)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, a.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = lib.lutgemm_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = lib.lutgemm_kernel_launch_count() - n0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sec = ms / 1e3
+    value = world * a.steps * rot * B / sec / 1e9
+    us_per_gemv = sec / (a.steps * rot) * 1e6
+
+    # end to end through the host-buffer entry point
+    e2e = None
+    if not a.no_e2e:
+        xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
+        yout = torch.empty((1, a.n), dtype=torch.int16).pin_memory()
+        def e2e_step():
+            for w in weights:
+                capi.check(lib.lutgemm_matmul_host(yout.data_ptr(), xin.data_ptr(), w.handle, 1), "matmul_host")
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if dist is not None:
+            t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e = {"value": world * a.steps * rot * B / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": rot * 2 * a.k,
+               "d2h_bytes_per_step": rot * 2 * a.n, "us_per_matvec": dt / (a.steps * rot) * 1e6}
+        # the result that came back is the device result
+        assert np.array_equal(yout.numpy(), ys[-1].cpu().view(torch.int16).numpy())
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    achieved = B / (us_per_gemv * 1e-6) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(3, a.warmup),
+        "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "matvecs_per_step": rot, "l2": f"{rot} distinct weight sets cycled "
+                   f"({rot * B / 1e6:.0f} MB per step, larger than L2)", "algorithmic_bytes_per_matvec": B,
+                   "parallelism": f"independent layers per rank x{world}"},
+        "us_per_matvec": us_per_gemv,
+        "packed_weight_GBps": a.n * a.k * a.q / 8 / (us_per_gemv * 1e-6) / 1e9,
+        "pct_of_8TBps_nominal": 100.0 * achieved / 8000.0,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_kind, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_lut_kernel"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if world == 1 and not a.no_cpu_baseline:
+        threads = 1
+        dt, kind, y_cpu = cpu_reference_gemv(a, threads)
+        # same seeds as weight set 0 of rank 0: the CPU result doubles as a live parity check
+        y_gpu = ys[0].float().cpu().numpy()
+        rms = float(np.sqrt((y_cpu ** 2).mean()))
+        line["cpu_baseline"] = {"value": B / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
+                                "sample": "one full matvec, single thread as the reference is written "
+                                          "(dequantize_cpu + serial-k fp32 matmul)", "seconds": dt,
+                                "max_abs_diff_vs_gpu_over_rms": float(np.abs(y_cpu - y_gpu).max() / rms)}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)

@@ -1,0 +1,152 @@
+/*
+ * lutgemm_b200 — C ABI of the B200 (sm_100a) LUT-GEMM library.
+ *
+ * Drop-in boundary for the BCQ matmul path of naver-aics/lut-gemm.  Every entry
+ * point is `extern "C"`, takes plain pointers and sizes, and returns an int
+ * status (LUTGEMM_OK == 0).  Beside each declaration is the reference interface
+ * it replaces, as <file>:<line> inside the reference project.
+ *
+ * Container layout (identical to the reference, column-wise mode):
+ *   bW      uint32 [K/32][q][N]   bit (k % 32) of bW[k/32][b][n] set <=> plane b of weight (k, n) is +1
+ *   alpha   fp16   [G][q][N]      G = num_groups, group size g = K / G along k
+ *   q_bias  fp16   [G][N]         optional per-group offset (uniform quantisation folded into BCQ)
+ *   y[m][n] = sum_g ( q_bias[g][n] * sum_{k in g} x[m][k]
+ *                     + sum_b alpha[g][b][n] * sum_{k in g} (+-1)(k,b,n) * x[m][k] )
+ * with N = mSize (output features), K = kSize (input features), q = nb.
+ */
+#ifndef LUTGEMM_B200_H
+#define LUTGEMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    LUTGEMM_OK = 0,
+    LUTGEMM_ERR_NULL = 1,          /* a required pointer is NULL */
+    LUTGEMM_ERR_SHAPE = 2,         /* K % 32 != 0, K % num_groups != 0, group size % 32 != 0, N < 1, ... */
+    LUTGEMM_ERR_BITS = 3,          /* num_bits outside 1..8 */
+    LUTGEMM_ERR_BATCH = 4,         /* m < 1 or above the supported maximum */
+    LUTGEMM_ERR_CUDA = 5,          /* a CUDA runtime call failed; see lutgemm_last_cuda_error() */
+    LUTGEMM_ERR_NO_DEVICE = 6,     /* no usable CUDA device: there is no CPU fallback */
+    LUTGEMM_ERR_TOO_LARGE = 7,     /* size beyond what the entry point supports */
+    LUTGEMM_ERR_ALIGN = 8          /* pointer not aligned as the entry point requires */
+};
+
+/* Opaque weight container.  Replaces class lutGEMM::nQWeight_fp16
+ * (lutGEMM/include/nQWeight_fp16.h:27-52). */
+typedef struct lutgemm_weight* lutgemm_weight_t;
+
+/* The public fields of the reference container (lutGEMM/include/nQWeight_fp16.h:29-37),
+ * as device pointers. */
+typedef struct lutgemm_weight_desc {
+    uint32_t* bWeight;   /* device, [K/32][q][N] */
+    void* alpha;         /* device fp16, [G][q][N] */
+    void* q_bias;        /* device fp16, [G][N], or NULL */
+    int num_groups;
+    int group_size;
+    int mSize;           /* N */
+    int kSize;           /* K */
+    int nb;              /* q */
+    int is_row_wise_quantize;
+    int device;
+} lutgemm_weight_desc;
+
+/* Uploads a container from host arrays to the current CUDA device.
+ * Replaces nQWeight_fp16::parsing (lutGEMM/src/nQWeight_fp16.cu:60-91) with the same
+ * argument meaning: bW [K/32][q][N] uint32; A float [G][q][N] and q_bias float [G][N]
+ * (or NULL) are rounded to fp16 (round-to-nearest-even); column-wise (is_row_wise == 0)
+ * means K = row, N = col; row-wise means N = row, K = col.
+ * The copy lives in plain device memory owned by the handle. */
+int lutgemm_weight_create(lutgemm_weight_t* out, const uint32_t* bW, const float* A,
+                          int row, int col, int num_bits, int is_row_wise,
+                          int num_alpha_groups, const float* q_bias);
+
+/* Same, from arrays that are already on the current device in their final types
+ * (uint32 planes, fp16 alpha, fp16 q_bias or NULL).  With copy == 0 the handle
+ * borrows the caller's buffers, which must outlive it.  No reference counterpart: the
+ * reference exposes its fields publicly (lutGEMM/include/nQWeight_fp16.h:29-37) and a caller
+ * would assign them by hand. */
+int lutgemm_weight_create_device(lutgemm_weight_t* out, const uint32_t* d_bW, const void* d_alpha_fp16,
+                                 const void* d_q_bias_fp16, int row, int col, int num_bits,
+                                 int is_row_wise, int num_alpha_groups, int copy);
+
+/* Replaces nQWeight_fp16::~nQWeight_fp16 (lutGEMM/src/nQWeight_fp16.cu:101-105); frees each
+ * owned buffer exactly once.  NULL is accepted. */
+int lutgemm_weight_destroy(lutgemm_weight_t w);
+
+/* Reads the container's fields (lutGEMM/include/nQWeight_fp16.h:29-37). */
+int lutgemm_weight_describe(lutgemm_weight_t w, lutgemm_weight_desc* desc);
+
+/* out[m][N] (fp16, device) = in[m][K] (fp16, device) x W.
+ * Replaces both lutGEMM::matmul overloads (lutGEMM/include/kernels.h:26-27,
+ * lutGEMM/src/kernels.cu:56-71); q_bias is applied whenever the container has one, for every m.
+ * Asynchronous on `stream` (a cudaStream_t, NULL = default stream); no host
+ * synchronisation.  Calls that share one handle use the handle's split-k workspace and must
+ * be ordered on one stream. */
+int lutgemm_matmul(void* out_fp16, const void* in_fp16, lutgemm_weight_t w, int m, void* stream);
+
+/* Same computation with the result left in fp32 (no final fp16 rounding). */
+int lutgemm_matmul_f32(float* out_f32, const void* in_fp16, lutgemm_weight_t w, int m, void* stream);
+
+/* Same computation from and to HOST buffers: copies in (m*K fp16) to the device, runs,
+ * copies out (m*N fp16) back and synchronises.  This is the call a host program holding
+ * CPU activations makes (the reference test keeps them in managed memory,
+ * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256). */
+int lutgemm_matmul_host(void* out_fp16_host, const void* in_fp16_host, lutgemm_weight_t w, int m);
+
+/* Dense fp16 weight on the device: W[k][N] (column-wise) or W[n][K] (row-wise),
+ * W = sum_b +-alpha, fp32 sum over planes b = 0..q-1 and one fp16 rounding, no q_bias.
+ * Replaces lutGEMM::dequantize_gpu (lutGEMM/src/nQWeight_fp16.cu:29-35) and is bit-identical to
+ * lutGEMM::dequantize_cpu (lutGEMM/src/nQWeight_fp16.cu:38-59). */
+int lutgemm_dequantize(lutgemm_weight_t w, void* d_fW_fp16, void* stream);
+
+/* Host packer: +-1 planes int8 [K][q][N] -> bW uint32 [K/32][q][N].
+ * Replaces makeRandomWeight's packing (tests/opt/fp16/int3_col_wise_matmul_fp16.cu:200-215). */
+int lutgemm_pack_planes(const int8_t* planes, int K, int q, int N, uint32_t* bW);
+
+/* Device packer: the same mapping with both arrays on the current device. */
+int lutgemm_pack_planes_device(const int8_t* d_planes, int K, int q, int N, uint32_t* d_bW, void* stream);
+
+/* Host converter, uniform quantisation -> BCQ with offset, written straight into the
+ * kernel layout.  Inputs in the Python examples' shapes: scale, zero float [N][G],
+ * code int32 [N][G][g] with values in [0, 2^q).  Outputs: bW [K/32][q][N] (plane b = bit b
+ * of the code), alpha float [G][q][N] = scale/2 * 2^b, q_bias float [G][N] =
+ * sum_b alpha_b - scale*zero.  Replaces RTNParameter.convert_bcq_format
+ * (examples/rtn_parameter.py:77-96) followed by the layout transposition the reference
+ * leaves to the caller. */
+int lutgemm_uniform_to_bcq(const float* scale, const float* zero, const int32_t* code,
+                           int N, int G, int g, int q, uint32_t* bW, float* alpha, float* q_bias);
+
+/* Device converter: same mapping, all arrays on the current device; alpha and q_bias are
+ * written as fp16 (the container's types), ready for lutgemm_weight_create_device. */
+int lutgemm_uniform_to_bcq_device(const float* d_scale, const float* d_zero, const int32_t* d_code,
+                                  int N, int G, int g, int q, uint32_t* d_bW, void* d_alpha_fp16,
+                                  void* d_q_bias_fp16, void* stream);
+
+/* The Python examples' tensors (alpha float [N][G][q], binary int8 [N][G][g][q] of +-1,
+ * offset float [N][G] or NULL; examples/bcq_parameter.py:41-48) -> kernel layout on the host. */
+int lutgemm_from_python_layout(const float* alpha_py, const int8_t* binary_py, const float* offset_py,
+                               int N, int K, int g, int q, uint32_t* bW, float* alpha, float* q_bias);
+
+/* The Python examples' uint8 interchange format (Packer.pack / Packer.unpack,
+ * examples/utils.py:162-181): L values of +-1 <-> L/8 bytes, byte j = sum_i 2^i * [flat[i*L/8 + j] > 0]. */
+int lutgemm_packer_pack(const int8_t* flat_pm1, size_t L, uint8_t* packed);
+int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat_pm1);
+
+/* Text for a status code; never NULL. */
+const char* lutgemm_status_string(int status);
+/* The cudaError_t of the last failing CUDA call on this thread (0 if none). */
+int lutgemm_last_cuda_error(void);
+/* How many kernels this library has launched in this process (all threads). */
+unsigned long long lutgemm_kernel_launch_count(void);
+/* Tuning knob: columns per CTA of the LUT matvec (0 = automatic).  Process-wide. */
+int lutgemm_set_gemv_ntile(int columns);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUTGEMM_B200_H */

@@ -1,0 +1,222 @@
+"""Python mirror of the reference's C++ interface for the BCQ matmul path, over the C ABI.
+
+Names and argument meaning follow the reference so that a test written against
+lutGEMM::nQWeight_fp16 / lutGEMM::matmul reads the same here:
+
+  nQWeight_fp16(bW, A, row, col, num_bits, is_row_wise_quantize, num_alpha_groups=1, q_bias=None)
+      lutGEMM/include/nQWeight_fp16.h:41-47, lutGEMM/src/nQWeight_fp16.cu:60-91 (parsing)
+  matmul(output, input, nqW, m)          lutGEMM/include/kernels.h:27, lutGEMM/src/kernels.cu:64-71
+  matmul_wx(output, nqW, input, n)       lutGEMM/include/kernels.h:26, lutGEMM/src/kernels.cu:56-63
+  dequantize_gpu(nqW, d_fW)              lutGEMM/include/nQWeight_fp16.h:24, lutGEMM/src/nQWeight_fp16.cu:29-35
+
+torch is used only to hold device memory and streams.  All arithmetic happens in the CUDA
+library; when it cannot run, calls raise LutGemmError.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+
+def _ptr(a):
+    """Device/host pointer of a torch tensor or numpy array (None -> NULL)."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        assert a.flags["C_CONTIGUOUS"]
+        return a.ctypes.data_as(C.c_void_p)
+    assert a.is_contiguous()
+    return C.c_void_p(a.data_ptr())
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream)
+
+
+class nQWeight_fp16:
+    """BCQ weight container on the current CUDA device.
+
+    bW: uint32 [K/32, q, N] (numpy);  A: float32 [G, q, N];  q_bias: float32 [G, N] or None.
+    Column-wise (is_row_wise_quantize False): K = row, N = col.  Fields keep the reference's names.
+    """
+
+    def __init__(self, bW=None, A=None, row=0, col=0, num_bits=0, is_row_wise_quantize=False,
+                 num_alpha_groups=1, q_bias=None):
+        self._h = C.c_void_p()
+        self._keep = None
+        if bW is not None:
+            self.parsing(bW, A, row, col, num_bits, is_row_wise_quantize, num_alpha_groups, q_bias)
+
+    def parsing(self, bW, A, row, col, num_bits, is_row_wise_quantize, num_alpha_groups=1, q_bias=None):
+        self.close()
+        bW = np.ascontiguousarray(bW, dtype=np.uint32)
+        A = np.ascontiguousarray(A, dtype=np.float32)
+        qb = None if q_bias is None else np.ascontiguousarray(q_bias, dtype=np.float32)
+        N, K = (row, col) if is_row_wise_quantize else (col, row)
+        if bW.size != (K // 32) * num_bits * N or A.size != num_alpha_groups * num_bits * N or \
+                (qb is not None and qb.size != num_alpha_groups * N):
+            raise ValueError("array sizes do not match (row, col, num_bits, num_alpha_groups)")
+        capi.check(capi.lib().lutgemm_weight_create(C.byref(self._h), _ptr(bW), _ptr(A), row, col, num_bits,
+                                                    int(bool(is_row_wise_quantize)), num_alpha_groups, _ptr(qb)),
+                   "nQWeight_fp16.parsing")
+        self._read_fields()
+        return self
+
+    @classmethod
+    def from_device(cls, d_bW, d_alpha_fp16, d_q_bias_fp16, row, col, num_bits, is_row_wise_quantize=False,
+                    num_alpha_groups=1, copy=False):
+        """Wraps (copy=False) or copies tensors that already live on the device in their final types."""
+        self = cls()
+        capi.check(capi.lib().lutgemm_weight_create_device(
+            C.byref(self._h), _ptr(d_bW), _ptr(d_alpha_fp16), _ptr(d_q_bias_fp16), row, col, num_bits,
+            int(bool(is_row_wise_quantize)), num_alpha_groups, int(bool(copy))), "nQWeight_fp16.from_device")
+        if not copy:
+            self._keep = (d_bW, d_alpha_fp16, d_q_bias_fp16)
+        self._read_fields()
+        return self
+
+    def _read_fields(self):
+        d = capi.WeightDesc()
+        capi.check(capi.lib().lutgemm_weight_describe(self._h, C.byref(d)), "describe")
+        self.bWeight, self.alpha, self.q_bias = d.bWeight, d.alpha, d.q_bias
+        self.num_groups, self.group_size = d.num_groups, d.group_size
+        self.mSize, self.kSize, self.nb = d.mSize, d.kSize, d.nb
+        self.is_row_wise_quantize = bool(d.is_row_wise_quantize)
+        self.device = d.device
+
+    @property
+    def handle(self):
+        if not self._h:
+            raise ValueError("empty nQWeight_fp16: call parsing() first")
+        return self._h
+
+    def getDequantiedWeight(self, onGPU=True):
+        """Dense fp16 weight as a torch CUDA tensor: [K, N] column-wise, [N, K] row-wise
+        (lutGEMM/src/nQWeight_fp16.cu:93-99).  Only the GPU path exists here."""
+        if not onGPU:
+            raise NotImplementedError("this library has no CPU path")
+        import torch
+        shape = (self.mSize, self.kSize) if self.is_row_wise_quantize else (self.kSize, self.mSize)
+        fW = torch.empty(shape, dtype=torch.float16, device=f"cuda:{self.device}")
+        dequantize_gpu(self, fW)
+        return fW
+
+    def close(self):
+        if self._h:
+            capi.lib().lutgemm_weight_destroy(self._h)
+            self._h = C.c_void_p()
+            self._keep = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def matmul(output, input, nqW, m, algo=0, stream=None):
+    """output[m, N] (fp16 CUDA tensor) = input[m, K] (fp16 CUDA tensor) x W.  `algo` is accepted and
+    ignored, as in the reference (lutGEMM/src/cuda/kernels/mv_fp16.hpp:121-128)."""
+    capi.check(capi.lib().lutgemm_matmul(_ptr(output), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)), "matmul")
+    return output
+
+
+def matmul_wx(output, nqW, input, n, algo=0, stream=None):
+    """The (output, nqW, input, n) overload; the same computation for the layouts this library takes."""
+    return matmul(output, input, nqW, n, algo, stream)
+
+
+def matmul_f32(output_f32, input, nqW, m, stream=None):
+    capi.check(capi.lib().lutgemm_matmul_f32(_ptr(output_f32), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)),
+               "matmul_f32")
+    return output_f32
+
+
+def matmul_host(output_np, input_np, nqW, m):
+    """Host-buffer form: numpy fp16 in, numpy fp16 out, copies included, synchronous."""
+    capi.check(capi.lib().lutgemm_matmul_host(_ptr(output_np), _ptr(input_np), nqW.handle, int(m)), "matmul_host")
+    return output_np
+
+
+def dequantize_gpu(nqW, d_fW, algo=0, stream=None):
+    capi.check(capi.lib().lutgemm_dequantize(nqW.handle, _ptr(d_fW), _stream_ptr(stream)), "dequantize_gpu")
+    return d_fW
+
+
+def pack_planes(planes):
+    """+-1 planes int8 [K, q, N] (numpy) -> bW uint32 [K/32, q, N]."""
+    planes = np.ascontiguousarray(planes, dtype=np.int8)
+    K, q, N = planes.shape
+    bW = np.empty((K // 32, q, N), np.uint32)
+    capi.check(capi.lib().lutgemm_pack_planes(_ptr(planes), K, q, N, _ptr(bW)), "pack_planes")
+    return bW
+
+
+def pack_planes_device(d_planes, stream=None):
+    import torch
+    K, q, N = d_planes.shape
+    bW = torch.empty((K // 32, q, N), dtype=torch.int32, device=d_planes.device)
+    capi.check(capi.lib().lutgemm_pack_planes_device(_ptr(d_planes), K, q, N, _ptr(bW), _stream_ptr(stream)),
+               "pack_planes_device")
+    return bW
+
+
+def uniform_to_bcq(scale, zero, code, q):
+    """scale, zero float32 [N, G]; code int32 [N, G, g] -> (bW [K/32, q, N], alpha [G, q, N], q_bias [G, N])."""
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    zero = np.ascontiguousarray(zero, dtype=np.float32)
+    code = np.ascontiguousarray(code, dtype=np.int32)
+    N, G, g = code.shape
+    bW = np.empty((G * g // 32, q, N), np.uint32)
+    alpha = np.empty((G, q, N), np.float32)
+    q_bias = np.empty((G, N), np.float32)
+    capi.check(capi.lib().lutgemm_uniform_to_bcq(_ptr(scale), _ptr(zero), _ptr(code), N, G, g, q, _ptr(bW), _ptr(alpha),
+                                                 _ptr(q_bias)), "uniform_to_bcq")
+    return bW, alpha, q_bias
+
+
+def uniform_to_bcq_device(d_scale, d_zero, d_code, q, stream=None):
+    """Same on the device; returns torch tensors (bW int32 view of the uint32 words, alpha fp16, q_bias fp16)."""
+    import torch
+    N, G, g = d_code.shape
+    dev = d_code.device
+    bW = torch.empty((G * g // 32, q, N), dtype=torch.int32, device=dev)
+    alpha = torch.empty((G, q, N), dtype=torch.float16, device=dev)
+    q_bias = torch.empty((G, N), dtype=torch.float16, device=dev)
+    capi.check(capi.lib().lutgemm_uniform_to_bcq_device(_ptr(d_scale), _ptr(d_zero), _ptr(d_code), N, G, g, q, _ptr(bW),
+                                                        _ptr(alpha), _ptr(q_bias), _stream_ptr(stream)),
+               "uniform_to_bcq_device")
+    return bW, alpha, q_bias
+
+
+def from_python_layout(alpha_py, binary_py, offset_py=None):
+    """alpha [N,G,q], binary int8 [N,G,g,q], offset [N,G] or None -> (bW, alpha [G,q,N], q_bias [G,N] or None)."""
+    alpha_py = np.ascontiguousarray(alpha_py, dtype=np.float32)
+    binary_py = np.ascontiguousarray(binary_py, dtype=np.int8)
+    off = None if offset_py is None else np.ascontiguousarray(offset_py, dtype=np.float32)
+    N, G, g, q = binary_py.shape
+    K = G * g
+    bW = np.empty((K // 32, q, N), np.uint32)
+    alpha = np.empty((G, q, N), np.float32)
+    q_bias = None if off is None else np.empty((G, N), np.float32)
+    capi.check(capi.lib().lutgemm_from_python_layout(_ptr(alpha_py), _ptr(binary_py), _ptr(off), N, K, g, q, _ptr(bW),
+                                                     _ptr(alpha), _ptr(q_bias)), "from_python_layout")
+    return bW, alpha, q_bias
+
+
+def packer_pack(flat_pm1):
+    flat = np.ascontiguousarray(flat_pm1, dtype=np.int8).reshape(-1)
+    out = np.empty(flat.size // 8, np.uint8)
+    capi.check(capi.lib().lutgemm_packer_pack(_ptr(flat), flat.size, _ptr(out)), "packer_pack")
+    return out
+
+
+def packer_unpack(packed, L):
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty(L, np.int8)
+    capi.check(capi.lib().lutgemm_packer_unpack(_ptr(packed), L, _ptr(out)), "packer_unpack")
+    return out

@@ -1,0 +1,86 @@
+"""ctypes binding of liblutgemm_b200.so (the C ABI in include/lutgemm_b200.h).
+
+The library is the product; nothing here computes.  If the shared library is missing it is
+built in-tree with nvcc; if that fails, or if a compute call finds no CUDA device, the error is
+raised: there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+from . import _build
+
+OK = 0
+ERR_NULL, ERR_SHAPE, ERR_BITS, ERR_BATCH, ERR_CUDA, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_ALIGN = range(1, 9)
+
+# every symbol include/lutgemm_b200.h declares
+SYMBOLS = (
+    "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
+    "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_dequantize",
+    "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
+    "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
+    "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
+)
+
+
+class WeightDesc(C.Structure):
+    _fields_ = [("bWeight", C.c_void_p), ("alpha", C.c_void_p), ("q_bias", C.c_void_p),
+                ("num_groups", C.c_int), ("group_size", C.c_int), ("mSize", C.c_int), ("kSize", C.c_int),
+                ("nb", C.c_int), ("is_row_wise_quantize", C.c_int), ("device", C.c_int)]
+
+
+class LutGemmError(RuntimeError):
+    def __init__(self, status, where):
+        self.status = status
+        msg = lib().lutgemm_status_string(status).decode()
+        cuda = lib().lutgemm_last_cuda_error()
+        super().__init__(f"{where}: status {status} ({msg})" + (f", cudaError {cuda}" if status in (ERR_CUDA, ERR_NO_DEVICE) else ""))
+
+
+_LIB = None
+
+
+def lib():
+    """Loads (building first if needed) the shared library and declares the prototypes."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.LIB
+    if _build.needs_build():
+        if os.path.exists(_build.NVCC):
+            _build.build()
+        elif not os.path.exists(path):
+            raise RuntimeError("liblutgemm_b200.so is missing and nvcc is not available to build it; "
+                               "lutgemm_b200 has no fallback implementation")
+    L = C.CDLL(path)
+    vp, ip = C.c_void_p, C.c_int
+    L.lutgemm_weight_create.argtypes = [C.POINTER(vp), vp, vp, ip, ip, ip, ip, ip, vp]
+    L.lutgemm_weight_create_device.argtypes = [C.POINTER(vp), vp, vp, vp, ip, ip, ip, ip, ip, ip]
+    L.lutgemm_weight_destroy.argtypes = [vp]
+    L.lutgemm_weight_describe.argtypes = [vp, C.POINTER(WeightDesc)]
+    L.lutgemm_matmul.argtypes = [vp, vp, vp, ip, vp]
+    L.lutgemm_matmul_f32.argtypes = [vp, vp, vp, ip, vp]
+    L.lutgemm_matmul_host.argtypes = [vp, vp, vp, ip]
+    L.lutgemm_dequantize.argtypes = [vp, vp, vp]
+    L.lutgemm_pack_planes.argtypes = [vp, ip, ip, ip, vp]
+    L.lutgemm_pack_planes_device.argtypes = [vp, ip, ip, ip, vp, vp]
+    L.lutgemm_uniform_to_bcq.argtypes = [vp, vp, vp, ip, ip, ip, ip, vp, vp, vp]
+    L.lutgemm_uniform_to_bcq_device.argtypes = [vp, vp, vp, ip, ip, ip, ip, vp, vp, vp, vp]
+    L.lutgemm_from_python_layout.argtypes = [vp, vp, vp, ip, ip, ip, ip, vp, vp, vp]
+    L.lutgemm_packer_pack.argtypes = [vp, C.c_size_t, vp]
+    L.lutgemm_packer_unpack.argtypes = [vp, C.c_size_t, vp]
+    L.lutgemm_status_string.argtypes = [ip]
+    L.lutgemm_status_string.restype = C.c_char_p
+    L.lutgemm_last_cuda_error.restype = ip
+    L.lutgemm_kernel_launch_count.restype = C.c_ulonglong
+    L.lutgemm_set_gemv_ntile.argtypes = [ip]
+    for name in SYMBOLS:
+        fn = getattr(L, name)
+        if name not in ("lutgemm_status_string", "lutgemm_kernel_launch_count"):
+            fn.restype = ip
+    _LIB = L
+    return L
+
+
+def check(status, where):
+    if status != OK:
+        raise LutGemmError(status, where)

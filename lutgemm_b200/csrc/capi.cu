@@ -1,0 +1,459 @@
+// C ABI of the library (declared in include/lutgemm_b200.h): container handle, argument checks,
+// kernel selection and launch.  There is no CPU fallback anywhere in this file: without a usable
+// CUDA device every compute entry point returns LUTGEMM_ERR_NO_DEVICE / LUTGEMM_ERR_CUDA.
+#include "../../include/lutgemm_b200.h"
+
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "aux_kernels.cuh"
+#include "gemv_lut.cuh"
+
+struct lutgemm_weight {
+    uint32_t* bW = nullptr;
+    __half* alpha = nullptr;
+    __half* q_bias = nullptr;
+    int N = 0, K = 0, q = 0, G = 0, g = 0;
+    bool row_wise = false;
+    bool owns = true;
+    int device = 0;
+    // split-k workspace: partial sums [ceil(K/512)][N] fp32 and per-tile arrival counters
+    float* partial = nullptr;
+    unsigned* counters = nullptr;
+    // staging for lutgemm_matmul_host
+    void* h_stage_in = nullptr;
+    void* d_stage_in = nullptr;
+    void* d_stage_out = nullptr;
+    size_t stage_rows = 0;
+};
+
+namespace {
+
+thread_local int g_last_cuda = 0;
+std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_ntile_override{0};
+constexpr int kMaxCounters = 4096;
+constexpr int kMaxBatch = 65536;
+
+#define LG_CUDA(call)                                  \
+    do {                                               \
+        cudaError_t e__ = (call);                      \
+        if (e__ != cudaSuccess) {                      \
+            g_last_cuda = (int)e__;                    \
+            return (e__ == cudaErrorNoDevice || e__ == cudaErrorInsufficientDriver) \
+                       ? LUTGEMM_ERR_NO_DEVICE : LUTGEMM_ERR_CUDA; \
+        }                                              \
+    } while (0)
+
+int check_shape(int row, int col, int q, int is_row_wise, int groups, int* N, int* K) {
+    if (row < 1 || col < 1 || groups < 1) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    *N = is_row_wise ? row : col;
+    *K = is_row_wise ? col : row;
+    if (*K % 32 != 0 || *K % groups != 0) return LUTGEMM_ERR_SHAPE;
+    if ((*K / groups) % 32 != 0) return LUTGEMM_ERR_SHAPE;
+    if ((long long)(*K / 32) * q * (long long)*N > (1ll << 40)) return LUTGEMM_ERR_TOO_LARGE;
+    return LUTGEMM_OK;
+}
+
+int alloc_workspace(lutgemm_weight* w) {
+    const size_t nslabs = (size_t)(w->K + lg::kSlabK - 1) / lg::kSlabK;
+    LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
+    LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
+    LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
+    return LUTGEMM_OK;
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+    }
+    return sms;
+}
+
+// Columns per CTA: enough CTAs to occupy every SM twice over, but wide enough that building the
+// 64 KB table stays a small part of a CTA's work.
+int choose_ntile(int N, int nslabs) {
+    int forced = g_ntile_override.load();
+    int ntile;
+    if (forced > 0) {
+        ntile = forced;
+    } else {
+        const int slots = 2 * sm_count();
+        int tiles = slots / nslabs;
+        if (tiles < 1) tiles = 1;
+        ntile = (N + tiles - 1) / tiles;
+        if (ntile < 512) ntile = 512;
+    }
+    ntile = (ntile + lg::kCtaCols - 1) / lg::kCtaCols * lg::kCtaCols;
+    while ((N + ntile - 1) / ntile > kMaxCounters) ntile *= 2;
+    return ntile;
+}
+
+template <int Q>
+int launch_gemv_q(const lg::GemvParams& p, dim3 grid, bool bias, cudaStream_t st) {
+    static bool configured[64][2] = {};   // the attribute is per device
+    auto kern = bias ? lg::gemv_lut_kernel<Q, true> : lg::gemv_lut_kernel<Q, false>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev][bias]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kLutBytes));
+        if (dev < 64) configured[dev][bias] = true;
+    }
+    kern<<<grid, lg::kGemvThreads, lg::kLutBytes, st>>>(p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+// One matvec row: y (fp16 and/or fp32) = x . W
+int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
+    const bool fast = (w->N % 4 == 0) && (w->K % 256 == 0);
+    if (!fast) {
+        dim3 grid((w->N + 127) / 128);
+        lg::gemv_generic_kernel<<<grid, 128, 0, st>>>(w->bW, w->alpha, w->q_bias, x, y16, y32, w->N, w->K, w->q, w->g);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        LG_CUDA(cudaGetLastError());
+        return LUTGEMM_OK;
+    }
+    lg::GemvParams p;
+    p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
+    p.partial = w->partial; p.counters = w->counters; p.y16 = y16; p.y32 = y32;
+    p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
+    p.nslabs = (w->K + lg::kSlabK - 1) / lg::kSlabK;
+    p.n_tile = choose_ntile(w->N, p.nslabs);
+    dim3 grid((w->N + p.n_tile - 1) / p.n_tile, p.nslabs);
+    const bool bias = w->q_bias != nullptr;
+    switch (w->q) {
+        case 1: return launch_gemv_q<1>(p, grid, bias, st);
+        case 2: return launch_gemv_q<2>(p, grid, bias, st);
+        case 3: return launch_gemv_q<3>(p, grid, bias, st);
+        case 4: return launch_gemv_q<4>(p, grid, bias, st);
+        case 5: return launch_gemv_q<5>(p, grid, bias, st);
+        case 6: return launch_gemv_q<6>(p, grid, bias, st);
+        case 7: return launch_gemv_q<7>(p, grid, bias, st);
+        case 8: return launch_gemv_q<8>(p, grid, bias, st);
+    }
+    return LUTGEMM_ERR_BITS;
+}
+
+int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int m, void* stream) {
+    if (!w || !in || (!y16 && !y32)) return LUTGEMM_ERR_NULL;
+    if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    if (((uintptr_t)in & 15) || ((uintptr_t)y16 & 15) || ((uintptr_t)y32 & 15)) return LUTGEMM_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const __half* x = (const __half*)in;
+    for (int r = 0; r < m; r++) {
+        int rc = gemv_row(w, x + (size_t)r * w->K, y16 ? y16 + (size_t)r * w->N : nullptr,
+                          y32 ? y32 + (size_t)r * w->N : nullptr, st);
+        if (rc != LUTGEMM_OK) return rc;
+    }
+    return LUTGEMM_OK;
+}
+
+int finish_create(lutgemm_weight* w, lutgemm_weight_t* out) {
+    int rc = alloc_workspace(w);
+    if (rc != LUTGEMM_OK) {
+        lutgemm_weight_destroy(w);
+        return rc;
+    }
+    *out = w;
+    return LUTGEMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lutgemm_weight_create(lutgemm_weight_t* out, const uint32_t* bW, const float* A, int row, int col,
+                          int num_bits, int is_row_wise, int num_alpha_groups, const float* q_bias) {
+    if (!out || !bW || !A) return LUTGEMM_ERR_NULL;
+    int N, K;
+    int rc = check_shape(row, col, num_bits, is_row_wise, num_alpha_groups, &N, &K);
+    if (rc != LUTGEMM_OK) return rc;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    lutgemm_weight* w = new (std::nothrow) lutgemm_weight();
+    if (!w) return LUTGEMM_ERR_TOO_LARGE;
+    w->N = N; w->K = K; w->q = num_bits; w->G = num_alpha_groups; w->g = K / num_alpha_groups;
+    w->row_wise = is_row_wise != 0; w->device = dev; w->owns = true;
+    const size_t n_words = (size_t)(K / 32) * num_bits * N;
+    const size_t n_alpha = (size_t)w->G * num_bits * N;
+    const size_t n_bias = (size_t)w->G * N;
+#define LG_TRY(call) do { cudaError_t e__ = (call); if (e__ != cudaSuccess) { g_last_cuda = (int)e__; lutgemm_weight_destroy(w); \
+        return (e__ == cudaErrorNoDevice) ? LUTGEMM_ERR_NO_DEVICE : LUTGEMM_ERR_CUDA; } } while (0)
+    LG_TRY(cudaMalloc(&w->bW, n_words * sizeof(uint32_t)));
+    LG_TRY(cudaMalloc(&w->alpha, n_alpha * sizeof(__half)));
+    LG_TRY(cudaMemcpy(w->bW, bW, n_words * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    {
+        std::vector<__half> tmp(n_alpha);
+        for (size_t i = 0; i < n_alpha; i++) tmp[i] = __float2half_rn(A[i]);
+        LG_TRY(cudaMemcpy(w->alpha, tmp.data(), n_alpha * sizeof(__half), cudaMemcpyHostToDevice));
+    }
+    if (q_bias) {
+        LG_TRY(cudaMalloc(&w->q_bias, n_bias * sizeof(__half)));
+        std::vector<__half> tmp(n_bias);
+        for (size_t i = 0; i < n_bias; i++) tmp[i] = __float2half_rn(q_bias[i]);
+        LG_TRY(cudaMemcpy(w->q_bias, tmp.data(), n_bias * sizeof(__half), cudaMemcpyHostToDevice));
+    }
+    return finish_create(w, out);
+}
+
+int lutgemm_weight_create_device(lutgemm_weight_t* out, const uint32_t* d_bW, const void* d_alpha,
+                                 const void* d_q_bias, int row, int col, int num_bits, int is_row_wise,
+                                 int num_alpha_groups, int copy) {
+    if (!out || !d_bW || !d_alpha) return LUTGEMM_ERR_NULL;
+    int N, K;
+    int rc = check_shape(row, col, num_bits, is_row_wise, num_alpha_groups, &N, &K);
+    if (rc != LUTGEMM_OK) return rc;
+    if (((uintptr_t)d_bW & 15) || ((uintptr_t)d_alpha & 15) || ((uintptr_t)d_q_bias & 15)) return LUTGEMM_ERR_ALIGN;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    lutgemm_weight* w = new (std::nothrow) lutgemm_weight();
+    if (!w) return LUTGEMM_ERR_TOO_LARGE;
+    w->N = N; w->K = K; w->q = num_bits; w->G = num_alpha_groups; w->g = K / num_alpha_groups;
+    w->row_wise = is_row_wise != 0; w->device = dev;
+    const size_t n_words = (size_t)(K / 32) * num_bits * N;
+    const size_t n_alpha = (size_t)w->G * num_bits * N;
+    const size_t n_bias = (size_t)w->G * N;
+    if (!copy) {
+        w->owns = false;
+        w->bW = const_cast<uint32_t*>(d_bW);
+        w->alpha = (__half*)const_cast<void*>(d_alpha);
+        w->q_bias = (__half*)const_cast<void*>(d_q_bias);
+    } else {
+        w->owns = true;
+        LG_TRY(cudaMalloc(&w->bW, n_words * sizeof(uint32_t)));
+        LG_TRY(cudaMalloc(&w->alpha, n_alpha * sizeof(__half)));
+        LG_TRY(cudaMemcpy(w->bW, d_bW, n_words * sizeof(uint32_t), cudaMemcpyDeviceToDevice));
+        LG_TRY(cudaMemcpy(w->alpha, d_alpha, n_alpha * sizeof(__half), cudaMemcpyDeviceToDevice));
+        if (d_q_bias) {
+            LG_TRY(cudaMalloc(&w->q_bias, n_bias * sizeof(__half)));
+            LG_TRY(cudaMemcpy(w->q_bias, d_q_bias, n_bias * sizeof(__half), cudaMemcpyDeviceToDevice));
+        }
+    }
+    return finish_create(w, out);
+}
+
+int lutgemm_weight_destroy(lutgemm_weight_t w) {
+    if (!w) return LUTGEMM_OK;
+    if (w->owns) {
+        if (w->bW) cudaFree(w->bW);
+        if (w->alpha) cudaFree(w->alpha);
+        if (w->q_bias) cudaFree(w->q_bias);
+    }
+    if (w->partial) cudaFree(w->partial);
+    if (w->counters) cudaFree(w->counters);
+    if (w->h_stage_in) cudaFreeHost(w->h_stage_in);
+    if (w->d_stage_in) cudaFree(w->d_stage_in);
+    if (w->d_stage_out) cudaFree(w->d_stage_out);
+    delete w;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_weight_describe(lutgemm_weight_t w, lutgemm_weight_desc* d) {
+    if (!w || !d) return LUTGEMM_ERR_NULL;
+    d->bWeight = w->bW; d->alpha = w->alpha; d->q_bias = w->q_bias;
+    d->num_groups = w->G; d->group_size = w->g; d->mSize = w->N; d->kSize = w->K; d->nb = w->q;
+    d->is_row_wise_quantize = w->row_wise ? 1 : 0; d->device = w->device;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_matmul(void* out, const void* in, lutgemm_weight_t w, int m, void* stream) {
+    if (!out) return LUTGEMM_ERR_NULL;
+    return matmul_impl((__half*)out, nullptr, in, w, m, stream);
+}
+
+int lutgemm_matmul_f32(float* out, const void* in, lutgemm_weight_t w, int m, void* stream) {
+    if (!out) return LUTGEMM_ERR_NULL;
+    return matmul_impl(nullptr, out, in, w, m, stream);
+}
+
+int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w, int m) {
+    if (!w || !out_host || !in_host) return LUTGEMM_ERR_NULL;
+    if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    if (w->stage_rows < (size_t)m) {
+        if (w->d_stage_in) cudaFree(w->d_stage_in);
+        if (w->d_stage_out) cudaFree(w->d_stage_out);
+        w->d_stage_in = w->d_stage_out = nullptr;
+        w->stage_rows = 0;
+        LG_CUDA(cudaMalloc(&w->d_stage_in, (size_t)m * w->K * sizeof(__half)));
+        LG_CUDA(cudaMalloc(&w->d_stage_out, (size_t)m * w->N * sizeof(__half)));
+        w->stage_rows = (size_t)m;
+    }
+    LG_CUDA(cudaMemcpyAsync(w->d_stage_in, in_host, (size_t)m * w->K * sizeof(__half), cudaMemcpyHostToDevice, 0));
+    int rc = matmul_impl((__half*)w->d_stage_out, nullptr, w->d_stage_in, w, m, nullptr);
+    if (rc != LUTGEMM_OK) return rc;
+    LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, 0));
+    LG_CUDA(cudaStreamSynchronize(0));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_dequantize(lutgemm_weight_t w, void* d_fW, void* stream) {
+    if (!w || !d_fW) return LUTGEMM_ERR_NULL;
+    if ((uintptr_t)d_fW & 15) return LUTGEMM_ERR_ALIGN;
+    dim3 grid((w->N + 255) / 256, w->K / 32);
+    if (grid.y > 65535) return LUTGEMM_ERR_TOO_LARGE;
+    lg::dequantize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w->bW, w->alpha, (__half*)d_fW, w->N, w->K, w->q,
+                                                                  w->g, w->row_wise ? 1 : 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_pack_planes(const int8_t* planes, int K, int q, int N, uint32_t* bW) {
+    if (!planes || !bW) return LUTGEMM_ERR_NULL;
+    if (K < 32 || K % 32 != 0 || N < 1) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    const size_t qn = (size_t)q * N;
+    for (int kw = 0; kw < K / 32; kw++) {
+        uint32_t* dst = bW + (size_t)kw * qn;
+        std::memset(dst, 0, qn * sizeof(uint32_t));
+        for (int t = 0; t < 32; t++) {
+            const int8_t* src = planes + (size_t)(kw * 32 + t) * qn;
+            const uint32_t bit = 1u << t;
+            for (size_t c = 0; c < qn; c++)
+                if (src[c] > 0) dst[c] |= bit;
+        }
+    }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_pack_planes_device(const int8_t* d_planes, int K, int q, int N, uint32_t* d_bW, void* stream) {
+    if (!d_planes || !d_bW) return LUTGEMM_ERR_NULL;
+    if (K < 32 || K % 32 != 0 || N < 1) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    dim3 grid((unsigned)(((size_t)q * N + 255) / 256), K / 32);
+    if (grid.y > 65535) return LUTGEMM_ERR_TOO_LARGE;
+    lg::pack_planes_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_planes, d_bW, K, q, N);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_uniform_to_bcq(const float* scale, const float* zero, const int32_t* code, int N, int G, int g, int q,
+                           uint32_t* bW, float* alpha, float* q_bias) {
+    if (!scale || !zero || !code || !bW || !alpha || !q_bias) return LUTGEMM_ERR_NULL;
+    if (N < 1 || G < 1 || g < 32 || g % 32 != 0) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    const int K = G * g;
+    std::memset(bW, 0, (size_t)(K / 32) * q * N * sizeof(uint32_t));
+    for (int n = 0; n < N; n++) {
+        for (int grp = 0; grp < G; grp++) {
+            const size_t ng = (size_t)n * G + grp;
+            const float z = scale[ng] * zero[ng];
+            const float half_s = scale[ng] / 2.0f;
+            float sum = 0.f;
+            for (int b = 0; b < q; b++) {
+                const float a = half_s * (float)(1u << b);
+                alpha[((size_t)grp * q + b) * N + n] = a;
+                sum += a;
+            }
+            q_bias[(size_t)grp * N + n] = sum - z;
+            const int32_t* c = code + ng * g;
+            for (int j = 0; j < g; j++) {
+                const int k = grp * g + j;
+                const int v = c[j];
+                for (int b = 0; b < q; b++)
+                    if ((v >> b) & 1) bW[((size_t)(k / 32) * q + b) * N + n] |= 1u << (k % 32);
+            }
+        }
+    }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_uniform_to_bcq_device(const float* d_scale, const float* d_zero, const int32_t* d_code, int N, int G,
+                                  int g, int q, uint32_t* d_bW, void* d_alpha, void* d_q_bias, void* stream) {
+    if (!d_scale || !d_zero || !d_code || !d_bW || !d_alpha || !d_q_bias) return LUTGEMM_ERR_NULL;
+    if (N < 1 || G < 1 || g < 32 || g % 32 != 0) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    dim3 grid((N + 255) / 256, (unsigned)((size_t)G * g / 32));
+    if (grid.y > 65535) return LUTGEMM_ERR_TOO_LARGE;
+    lg::uniform_to_bcq_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_scale, d_zero, d_code, N, G, g, q, d_bW,
+                                                                      (__half*)d_alpha, (__half*)d_q_bias);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_from_python_layout(const float* alpha_py, const int8_t* binary_py, const float* offset_py, int N, int K,
+                               int g, int q, uint32_t* bW, float* alpha, float* q_bias) {
+    if (!alpha_py || !binary_py || !bW || !alpha) return LUTGEMM_ERR_NULL;
+    if (offset_py && !q_bias) return LUTGEMM_ERR_NULL;
+    if (N < 1 || K < 32 || K % 32 != 0 || g < 1 || K % g != 0) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    const int G = K / g;
+    std::memset(bW, 0, (size_t)(K / 32) * q * N * sizeof(uint32_t));
+    for (int n = 0; n < N; n++)
+        for (int grp = 0; grp < G; grp++) {
+            const size_t ng = (size_t)n * G + grp;
+            if (offset_py) q_bias[(size_t)grp * N + n] = offset_py[ng];
+            for (int b = 0; b < q; b++) alpha[((size_t)grp * q + b) * N + n] = alpha_py[ng * q + b];
+            const int8_t* bin = binary_py + ng * g * q;
+            for (int j = 0; j < g; j++) {
+                const int k = grp * g + j;
+                for (int b = 0; b < q; b++)
+                    if (bin[(size_t)j * q + b] > 0) bW[((size_t)(k / 32) * q + b) * N + n] |= 1u << (k % 32);
+            }
+        }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_packer_pack(const int8_t* flat, size_t L, uint8_t* packed) {
+    if (!flat || !packed) return LUTGEMM_ERR_NULL;
+    if (L % 8 != 0) return LUTGEMM_ERR_SHAPE;
+    const size_t cols = L / 8;
+    std::memset(packed, 0, cols);
+    for (int i = 0; i < 8; i++) {
+        const int8_t* src = flat + (size_t)i * cols;
+        const uint8_t bit = (uint8_t)(1u << i);
+        for (size_t j = 0; j < cols; j++)
+            if (src[j] > 0) packed[j] |= bit;
+    }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat) {
+    if (!flat || !packed) return LUTGEMM_ERR_NULL;
+    if (L % 8 != 0) return LUTGEMM_ERR_SHAPE;
+    const size_t cols = L / 8;
+    for (int i = 0; i < 8; i++) {
+        int8_t* dst = flat + (size_t)i * cols;
+        for (size_t j = 0; j < cols; j++) dst[j] = ((packed[j] >> i) & 1) ? 1 : -1;
+    }
+    return LUTGEMM_OK;
+}
+
+const char* lutgemm_status_string(int s) {
+    switch (s) {
+        case LUTGEMM_OK: return "ok";
+        case LUTGEMM_ERR_NULL: return "a required pointer is NULL";
+        case LUTGEMM_ERR_SHAPE: return "unsupported shape (K % 32, K % num_groups, group size % 32, sizes >= 1)";
+        case LUTGEMM_ERR_BITS: return "num_bits must be in 1..8";
+        case LUTGEMM_ERR_BATCH: return "batch size out of range";
+        case LUTGEMM_ERR_CUDA: return "a CUDA call failed (see lutgemm_last_cuda_error)";
+        case LUTGEMM_ERR_NO_DEVICE: return "no usable CUDA device; this library has no CPU fallback";
+        case LUTGEMM_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        case LUTGEMM_ERR_ALIGN: return "pointer or row pitch not 16-byte aligned";
+    }
+    return "unknown status";
+}
+
+int lutgemm_last_cuda_error(void) { return g_last_cuda; }
+unsigned long long lutgemm_kernel_launch_count(void) { return g_launches.load(); }
+int lutgemm_set_gemv_ntile(int columns) {
+    if (columns < 0) return LUTGEMM_ERR_SHAPE;
+    g_ntile_override.store(columns);
+    return LUTGEMM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,228 @@
+"""GPU parity tests: the CUDA library, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Integer/bit work (packer, converter, dense dequantisation) is bit-exact; the matmul
+is within max-relative-error 1e-2 and mean-absolute-error 1e-3 of the reference's host
+dequant-and-matmul result."""
+import os
+
+import numpy as np
+import pytest
+
+import lutgemm_b200 as L
+from lutgemm_b200 import capi, synth
+from oracle import oracle
+from parity_utils import MAE, MAX_REL, error_metrics
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def dev_x(x):
+    return torch.from_numpy(x.view(np.int16)).cuda().view(torch.float16)
+
+
+def run_matmul(bW, alpha, q_bias, g, x, f32=False):
+    K = bW.shape[0] * 32
+    q, N = bW.shape[1], bW.shape[2]
+    w = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g, q_bias)
+    m = x.shape[0]
+    xd = dev_x(x)
+    if f32:
+        out = torch.empty((m, N), dtype=torch.float32, device="cuda")
+        L.matmul_f32(out, xd, w, m)
+    else:
+        out = torch.empty((m, N), dtype=torch.float16, device="cuda")
+        L.matmul(out, xd, w, m)
+    torch.cuda.synchronize()
+    y = out.float().cpu().numpy()
+    w.close()
+    return y
+
+
+def oracle_y(bW, alpha, q_bias, g, x):
+    return oracle.bcq_matmul_ref(x, bW, alpha.astype(np.float16), None if q_bias is None else q_bias.astype(np.float16), g)
+
+
+def check(y, ref, K, what, fp32_out=False):
+    rel, mae = error_metrics(y, ref)
+    assert rel <= MAX_REL, f"{what}: max rel err {rel:.3e}"
+    if fp32_out or K <= 12288:
+        assert mae <= MAE, f"{what}: MAE {mae:.3e}"
+    return rel, mae
+
+
+# ---- exhaustive small shapes: every q, odd column counts (generic kernel), table kernel with tails
+@pytest.mark.parametrize("q", list(range(1, 9)))
+@pytest.mark.parametrize("N,K,g", [(2, 32, 32), (6, 64, 32), (10, 96, 32), (33, 128, 64), (64, 256, 128),
+                                   (132, 768, 128), (128, 512, 32), (260, 1280, 256), (20, 256, 64)])
+def test_small_shapes_all_planes(q, N, K, g):
+    for bias in (False, True):
+        bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=synth.seed_for("small", N, K, q, bias), with_bias=bias,
+                                        signed_alpha=True, alpha_std=0.05)
+        x = synth.activations(1, K, seed=N + K)
+        ref = oracle_y(bW, alpha, qb, g, x)
+        check(run_matmul(bW, alpha, qb, g, x), ref, K, f"fp16 N={N} K={K} q={q} bias={bias}")
+        check(run_matmul(bW, alpha, qb, g, x, f32=True), ref, K, f"fp32 N={N} K={K} q={q} bias={bias}", fp32_out=True)
+
+
+def test_config1_4096_q3_g128():
+    N = K = 4096
+    bW, alpha, _ = synth.bcq_layer(N, K, 3, 128, seed=synth.seed_for("cfg1", N, K, 3))
+    x = synth.activations(1, K, seed=1)
+    ref = oracle_y(bW, alpha, None, 128, x)
+    rel, mae = check(run_matmul(bW, alpha, None, 128, x), ref, K, "config1")
+    f64 = oracle.bcq_matmul_f64(x, bW, alpha.astype(np.float16), None, 128)
+    rel64, mae64 = error_metrics(run_matmul(bW, alpha, None, 128, x, f32=True), f64)
+    assert rel64 < 1e-4 and mae64 < 1e-5      # the fp32 result is essentially exact
+
+
+def _sampled_columns_check(N, K, q, g, bias, tag, n_cols=192, uniform=False):
+    """Full-size layer on the GPU; the oracle recomputes a seeded sample of columns from a column-sliced
+    container (columns are independent), so the check runs at the benchmark sizes in seconds."""
+    seed = synth.seed_for(tag, N, K, q)
+    if uniform:
+        scale, zero, code = synth.uniform_layer(N, K, q, g, seed)
+        bW, alpha, qb = L.uniform_to_bcq(scale, zero, code, q)
+    else:
+        bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed, with_bias=bias)
+    x = synth.activations(1, K, seed=seed ^ 77)
+    y16 = run_matmul(bW, alpha, qb, g, x)
+    y32 = run_matmul(bW, alpha, qb, g, x, f32=True)
+    cols = np.sort(np.random.default_rng(seed).choice(N, size=n_cols, replace=False))
+    ref = oracle_y(np.ascontiguousarray(bW[:, :, cols]), np.ascontiguousarray(alpha[:, :, cols]),
+                   None if qb is None else np.ascontiguousarray(qb[:, cols]), g, x)
+    rel, mae = error_metrics(y16[:, cols], ref)
+    rel32, mae32 = error_metrics(y32[:, cols], ref)
+    assert rel <= MAX_REL and rel32 <= MAX_REL, (tag, rel, rel32)
+    assert mae32 <= MAE, (tag, mae32)
+    if K <= 12288:
+        assert mae <= MAE, (tag, mae)
+    # the fp16 output is the fp32 output rounded once
+    assert np.array_equal(y16, y32.astype(np.float16).astype(np.float32))
+    return y32
+
+
+@pytest.mark.parametrize("N,K", [(12288, 12288), (36864, 12288), (49152, 12288), (12288, 49152)])
+@pytest.mark.parametrize("q", [3, 4])
+def test_config2_opt175b_linears(N, K, q):
+    _sampled_columns_check(N, K, q, 128, False, "cfg2")
+
+
+@pytest.mark.parametrize("N,K", [(8192, 8192), (28672, 8192), (8192, 28672)])
+def test_config3_uniform4bit_llama70b(N, K):
+    _sampled_columns_check(N, K, 4, 128, True, "cfg3", uniform=True)
+
+
+def test_reference_benchmark_shape_7168():
+    # the shape of the reference's own benchmark TEST (tests/opt/fp16/int3_col_wise_matmul_fp16.cu:292-314)
+    _sampled_columns_check(28672, 7168, 3, 128, True, "ref-bench")
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 16, 32, 64, 128])
+def test_config4_batch_sweep(m):
+    N = K = 8192
+    bW, alpha, _ = synth.bcq_layer(N, K, 2, 64, seed=synth.seed_for("cfg4", N, K, 2))
+    x = synth.activations(m, K, seed=m)
+    y = run_matmul(bW, alpha, None, 64, x)
+    cols = np.arange(0, N, 61)
+    ref = oracle_y(np.ascontiguousarray(bW[:, :, cols]), np.ascontiguousarray(alpha[:, :, cols]), None, 64, x)
+    rel, mae = error_metrics(y[:, cols], ref)
+    assert rel <= MAX_REL and mae <= MAE, (m, rel, mae)
+
+
+def test_linearity_and_determinism_at_full_size():
+    N, K, q, g = 12288, 12288, 3, 128
+    bW, alpha, _ = synth.bcq_layer(N, K, q, g, seed=3)
+    w = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g)
+    x1 = synth.activations(1, K, seed=10).astype(np.float32)
+    x2 = synth.activations(1, K, seed=11).astype(np.float32)
+    xs = [(x1 * 0.5).astype(np.float16), (x2 * 0.25).astype(np.float16), (x1 * 0.5 + x2 * 0.25).astype(np.float16)]
+    ys = []
+    for x in xs:
+        out = torch.empty((1, N), dtype=torch.float32, device="cuda")
+        L.matmul_f32(out, dev_x(x), w, 1)
+        out2 = torch.empty((1, N), dtype=torch.float32, device="cuda")
+        L.matmul_f32(out2, dev_x(x), w, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)               # run-to-run bit identical
+        ys.append(out.cpu().numpy().astype(np.float64))
+    # x3 = fp16(x1/2 + x2/4) differs from the exact sum by fp16 rounding only
+    scale = np.sqrt((ys[2] ** 2).mean())
+    assert np.abs(ys[0] + ys[1] - ys[2]).max() <= 5e-3 * scale
+    w.close()
+
+
+@pytest.mark.parametrize("N,K,q,g,row_wise", [(64, 128, 3, 32, False), (48, 256, 4, 128, False), (130, 96, 8, 32, False),
+                                              (32, 128, 2, 128, True), (257, 512, 5, 64, True), (4096, 1024, 3, 128, False)])
+def test_dequantize_bit_exact(N, K, q, g, row_wise):
+    bW, alpha, _ = synth.bcq_layer(N, K, q, g, seed=N * 7 + K, signed_alpha=True)
+    row, col = (N, K) if row_wise else (K, N)
+    w = L.nQWeight_fp16(bW, alpha, row, col, q, row_wise, K // g)
+    fW = w.getDequantiedWeight().cpu().numpy()
+    ref = oracle.dequantize_cpu(bW, alpha.astype(np.float16), g, row_wise)
+    assert fW.shape == ref.shape
+    assert np.array_equal(fW.view(np.uint16), ref.view(np.uint16))
+    w.close()
+
+
+def test_dequantize_matches_reference_fixture(golden_dir):
+    z = np.load(os.path.join(golden_dir, "dequantize_cpu_reference.npz"))
+    for t in sorted({k.split("_")[0] for k in z.files}):
+        bW, a, g, rw = z[f"{t}_bW"], z[f"{t}_alpha"].astype(np.float32), int(z[f"{t}_g"]), bool(z[f"{t}_row_wise"])
+        K, q, N = bW.shape[0] * 32, bW.shape[1], bW.shape[2]
+        row, col = (N, K) if rw else (K, N)
+        w = L.nQWeight_fp16(bW, a, row, col, q, rw, K // g)
+        got = w.getDequantiedWeight().cpu().numpy()
+        assert np.array_equal(got.view(np.uint16), z[f"{t}_W"].view(np.uint16)), t
+        w.close()
+
+
+def test_device_packer_and_converter_bit_exact():
+    rng = np.random.default_rng(2)
+    K, q, N = 256, 3, 200
+    planes = (rng.integers(0, 2, size=(K, q, N)) * 2 - 1).astype(np.int8)
+    got = L.pack_planes_device(torch.from_numpy(planes).cuda()).cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, oracle.pack_planes(planes))
+    scale, zero, code = synth.uniform_layer(72, 512, 4, 128, seed=4)
+    bW_d, a_d, qb_d = L.uniform_to_bcq_device(torch.from_numpy(scale).cuda(), torch.from_numpy(zero).cuda(),
+                                              torch.from_numpy(code).cuda(), 4)
+    bW_h, a_h, qb_h = L.uniform_to_bcq(scale, zero, code, 4)
+    assert np.array_equal(bW_d.cpu().numpy().view(np.uint32), bW_h)
+    assert np.array_equal(a_d.cpu().numpy(), a_h.astype(np.float16))
+    assert np.array_equal(qb_d.cpu().numpy(), qb_h.astype(np.float16))
+
+
+def test_host_buffer_call_and_borrowed_device_container():
+    N, K, q, g = 1024, 1024, 3, 128
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=8, with_bias=True)
+    x = synth.activations(2, K, seed=5)
+    w = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g, qb)
+    y = np.empty((2, N), np.float16)
+    L.matmul_host(y, x, w, 2)
+    ref = oracle_y(bW, alpha, qb, g, x)
+    check(y.astype(np.float32), ref, K, "matmul_host")
+    # the same container built from device tensors without a copy
+    d_bW = torch.from_numpy(bW.view(np.int32)).cuda()
+    d_a = torch.from_numpy(alpha.astype(np.float16)).cuda()
+    d_qb = torch.from_numpy(qb.astype(np.float16)).cuda()
+    w2 = L.nQWeight_fp16.from_device(d_bW, d_a, d_qb, K, N, q, False, K // g, copy=False)
+    out = torch.empty((2, N), dtype=torch.float16, device="cuda")
+    L.matmul(out, dev_x(x), w2, 2)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), y)
+    assert w2.mSize == N and w2.kSize == K and w2.nb == q and w2.num_groups == K // g and w2.group_size == g
+    w.close(); w2.close()
+
+
+def test_bad_runtime_arguments_return_status():
+    bW, alpha, _ = synth.bcq_layer(64, 256, 2, 64, seed=1)
+    w = L.nQWeight_fp16(bW, alpha, 256, 64, 2, False, 4)
+    x = dev_x(synth.activations(1, 256, seed=1))
+    out = torch.empty((1, 64), dtype=torch.float16, device="cuda")
+    lib = capi.lib()
+    assert lib.lutgemm_matmul(out.data_ptr(), x.data_ptr(), w.handle, 0, None) == capi.ERR_BATCH
+    assert lib.lutgemm_matmul(out.data_ptr(), x.data_ptr() + 2, w.handle, 1, None) == capi.ERR_ALIGN
+    assert lib.lutgemm_matmul(None, x.data_ptr(), w.handle, 1, None) == capi.ERR_NULL
+    n0 = lib.lutgemm_kernel_launch_count()
+    L.matmul(out, x, w, 1)
+    assert lib.lutgemm_kernel_launch_count() == n0 + 1
+    w.close()
