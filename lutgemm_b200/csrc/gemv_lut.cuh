@@ -64,14 +64,14 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// The table is addressed as bytes from the start of the CTA's dynamic shared memory; plain C++
+// accesses let the compiler schedule the lookups freely between barriers.
 template <int IMM>
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
-    return v;
+__device__ __forceinline__ float lds_f32(const unsigned char* lut, uint32_t off) {
+    return *reinterpret_cast<const float*>(lut + off + IMM);
 }
-__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v));
+__device__ __forceinline__ void sts_f32(unsigned char* lut, uint32_t off, float v) {
+    *reinterpret_cast<float*>(lut + off) = v;
 }
 __device__ __forceinline__ float2 h2_to_f2(uint32_t u) {
     __half2 h = *reinterpret_cast<__half2*>(&u);
@@ -81,7 +81,7 @@ __device__ __forceinline__ float2 h2_to_f2(uint32_t u) {
 // Builds lut[idx][slot] for the 64 chunks of one slab.  Thread t owns chunk (t & 63) and the 64
 // entries idx in [64 * (t >> 6), +64), walked in Gray-code order so that each entry is one add away
 // from the previous one.  A warp stores 32 consecutive slots of one idx row: conflict free.
-__device__ __forceinline__ void build_lut(uint32_t lut_base, const __half* x, int k0, int K, int tid) {
+__device__ __forceinline__ void build_lut(unsigned char* lut, const __half* x, int k0, int K, int tid) {
     const int j = tid & 63, part = tid >> 6;
     float xv[8];
     {
@@ -93,15 +93,15 @@ __device__ __forceinline__ void build_lut(uint32_t lut_base, const __half* x, in
     float e = -xv[0] - xv[1] - xv[2] - xv[3] - xv[4] - xv[5];
     e += (part & 1) ? xv[6] : -xv[6];
     e += (part & 2) ? xv[7] : -xv[7];
-    const uint32_t base = lut_base + (uint32_t)part * (64u * 256u) + (uint32_t)j * 4u;
-    sts_f32(base, e);
+    const uint32_t base = (uint32_t)part * (64u * 256u) + (uint32_t)j * 4u;
+    sts_f32(lut, base, e);
 #pragma unroll
     for (int c = 1; c < 64; c++) {
         const int t = (c & 1) ? 0 : (c & 2) ? 1 : (c & 4) ? 2 : (c & 8) ? 3 : (c & 16) ? 4 : 5;   // bit flipped between gray(c-1) and gray(c)
         const int gcode = c ^ (c >> 1);
         const float two_x = 2.0f * xv[t];
         e = ((gcode >> t) & 1) ? e + two_x : e - two_x;
-        sts_f32(base + (uint32_t)gcode * 256u, e);
+        sts_f32(lut, base + (uint32_t)gcode * 256u, e);
     }
 }
 
@@ -109,8 +109,7 @@ __device__ __forceinline__ void build_lut(uint32_t lut_base, const __half* x, in
 template <int Q, bool BIAS>
 __global__ void __launch_bounds__(kGemvThreads, (Q <= 4) ? 2 : 1)
 gemv_lut_kernel(const GemvParams p) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    const uint32_t lut_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    extern __shared__ __align__(1024) unsigned char lut[];
     __shared__ int s_is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -166,7 +165,7 @@ gemv_lut_kernel(const GemvParams p) {
     int n = n_begin + warp * kWarpCols + 4 * r;
     load_block(n, w, al, qb);           // in flight while the table is built
 
-    build_lut(lut_base, p.x, k0, p.K, tid);
+    build_lut(lut, p.x, k0, p.K, tid);
     __syncthreads();
 
     // sum of the 32 activations under each of this lane's words: 4 entries idx = 255
@@ -174,8 +173,8 @@ gemv_lut_kernel(const GemvParams p) {
     if (BIAS) {
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            const uint32_t ad = lut_base + 255u * 256u + (uint32_t)(32 * i + 4 * a) * 4u;
-            xs[i] = lds_f32<0>(ad) + lds_f32<4>(ad) + lds_f32<8>(ad) + lds_f32<12>(ad);
+            const uint32_t ad = 255u * 256u + (uint32_t)(32 * i + 4 * a) * 4u;
+            xs[i] = lds_f32<0>(lut, ad) + lds_f32<4>(lut, ad) + lds_f32<8>(lut, ad) + lds_f32<12>(lut, ad);
         }
     }
 
@@ -200,15 +199,15 @@ gemv_lut_kernel(const GemvParams p) {
                 for (int c = 0; c < 4; c++) {
                     float t;
                     if (i == 0) {
-                        t = lds_f32<0>(lut_base + prmt(ww[c], cs, sel[0]));
-                        t += lds_f32<0>(lut_base + prmt(ww[c], cs, sel[1]));
-                        t += lds_f32<0>(lut_base + prmt(ww[c], cs, sel[2]));
-                        t += lds_f32<0>(lut_base + prmt(ww[c], cs, sel[3]));
+                        t = lds_f32<0>(lut, prmt(ww[c], cs, sel[0]));
+                        t += lds_f32<0>(lut, prmt(ww[c], cs, sel[1]));
+                        t += lds_f32<0>(lut, prmt(ww[c], cs, sel[2]));
+                        t += lds_f32<0>(lut, prmt(ww[c], cs, sel[3]));
                     } else {
-                        t = lds_f32<128>(lut_base + prmt(ww[c], cs, sel[0]));
-                        t += lds_f32<128>(lut_base + prmt(ww[c], cs, sel[1]));
-                        t += lds_f32<128>(lut_base + prmt(ww[c], cs, sel[2]));
-                        t += lds_f32<128>(lut_base + prmt(ww[c], cs, sel[3]));
+                        t = lds_f32<128>(lut, prmt(ww[c], cs, sel[0]));
+                        t += lds_f32<128>(lut, prmt(ww[c], cs, sel[1]));
+                        t += lds_f32<128>(lut, prmt(ww[c], cs, sel[2]));
+                        t += lds_f32<128>(lut, prmt(ww[c], cs, sel[3]));
                     }
                     acc[c] = fmaf(t, av[c], acc[c]);
                 }

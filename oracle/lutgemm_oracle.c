@@ -164,6 +164,34 @@ void lgo_bcq_matmul_ref(const uint16_t* x, const uint32_t* bW, const uint16_t* a
     }
 }
 
+/* The reference's fp32 host result, test-side semantics, never materialising W:
+ *   W[k][n] = q_bias[k/g][n] + sum_b alpha[k/g][b][n] * plane[k][b][n]     (dequantizeFrom_qW,
+ *             tests/opt/fp16/int3_col_wise_matmul_fp16.cu:235-244; fp32, b ascending)
+ *   y[m][n] = sum_k x[m][k] * W[k][n]                                      (matmul_cpu, :174-183; fp32, k ascending)
+ * alpha and q_bias are the container's fp16 values (what parsing stores, lutGEMM/src/nQWeight_fp16.cu:81,85)
+ * widened to float; x is the fp16 activation widened to float.  This is the "fp32 reference" the
+ * matvec tolerance is stated against. */
+void lgo_bcq_matmul_fp32(const uint16_t* x, const uint32_t* bW, const uint16_t* alpha,
+                         const uint16_t* q_bias, int M, int N, int K, int q, int group_size,
+                         float* y) {
+    for (int m = 0; m < M; m++) {
+#pragma omp parallel for schedule(static)
+        for (int n = 0; n < N; n++) {
+            float acc = 0.0f;
+            for (int k = 0; k < K; k++) {
+                int g = k / group_size;
+                float w = q_bias ? h2f(q_bias[(size_t)g * N + n]) : 0.0f;
+                for (int b = 0; b < q; b++) {
+                    float s = ((bW[((size_t)(k / 32) * q + b) * N + n] >> (k % 32)) & 1) ? 1.0f : -1.0f;
+                    w += h2f(alpha[((size_t)g * q + b) * N + n]) * s;
+                }
+                acc += h2f(x[(size_t)m * K + k]) * w;
+            }
+            y[(size_t)m * N + n] = acc;
+        }
+    }
+}
+
 /* Independent restatement in double precision with no intermediate fp16
  * rounding of W; bounds the oracle's own rounding error. */
 void lgo_bcq_matmul_f64(const uint16_t* x, const uint32_t* bW, const uint16_t* alpha,

@@ -54,6 +54,7 @@ def lib():
         L.lgo_dequantize_from_qw.argtypes = [_u32p, _f32p, vp, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
         L.lgo_matmul_cpu.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
         L.lgo_bcq_matmul_ref.argtypes = [_u16p, _u32p, _u16p, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
+        L.lgo_bcq_matmul_fp32.argtypes = [_u16p, _u32p, _u16p, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
         L.lgo_bcq_matmul_f64.argtypes = [_u16p, _u32p, _u16p, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f64p]
         L.lgo_uniform_to_bcq.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _i8p, _f32p]
         L.lgo_python_to_kernel_layout.argtypes = [_f32p, _i8p, vp, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _u32p, vp]
@@ -63,7 +64,7 @@ def lib():
         L.lgo_set_num_threads.argtypes = [C.c_int]
         for f in ("lgo_float_to_half", "lgo_half_to_float", "lgo_pack_planes", "lgo_unpack_planes",
                   "lgo_dequantize_cpu", "lgo_dequantize_from_qw", "lgo_matmul_cpu", "lgo_bcq_matmul_ref",
-                  "lgo_bcq_matmul_f64", "lgo_uniform_to_bcq", "lgo_python_to_kernel_layout",
+                  "lgo_bcq_matmul_f64", "lgo_bcq_matmul_fp32", "lgo_uniform_to_bcq", "lgo_python_to_kernel_layout",
                   "lgo_packer_pack", "lgo_packer_unpack", "lgo_set_num_threads"):
             getattr(L, f).restype = None
         _LIB = L
@@ -153,8 +154,22 @@ def matmul_cpu(x_f32, W_f32):
     return out
 
 
+def bcq_matmul_fp32(x_h, bW, alpha_h, q_bias_h, group_size):
+    """The reference's fp32 host result (test-side dequantizeFrom_qW + matmul_cpu), fp32 [M, N]."""
+    bW = np.ascontiguousarray(bW, dtype=np.uint32)
+    KW, q, N = bW.shape
+    K = KW * 32
+    x = _h(x_h).reshape(-1, K)
+    M = x.shape[0]
+    y = np.empty((M, N), np.float32)
+    qb = None if q_bias_h is None else _h(q_bias_h)
+    lib().lgo_bcq_matmul_fp32(x, bW, _h(alpha_h), qb.ctypes.data_as(C.c_void_p) if qb is not None else None,
+                              M, N, K, q, int(group_size), y)
+    return y
+
+
 def bcq_matmul_ref(x_h, bW, alpha_h, q_bias_h, group_size):
-    """The reference's host dequant-and-matmul result, fp32 [M, N]."""
+    """The host result through the library's dequantize_cpu (W rounded to fp16) plus the offset term, fp32 [M, N]."""
     bW = np.ascontiguousarray(bW, dtype=np.uint32)
     KW, q, N = bW.shape
     K = KW * 32

@@ -10,7 +10,7 @@ import pytest
 import lutgemm_b200 as L
 from lutgemm_b200 import capi, synth
 from oracle import oracle
-from parity_utils import MAE, MAX_REL, error_metrics
+from parity_utils import MAE, MAX_REL, REF16_FLOOR, error_metrics
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -39,6 +39,12 @@ def run_matmul(bW, alpha, q_bias, g, x, f32=False):
 
 
 def oracle_y(bW, alpha, q_bias, g, x):
+    """fp32 host dequant-and-matmul (test-side semantics of the reference)."""
+    return oracle.bcq_matmul_fp32(x, bW, alpha.astype(np.float16), None if q_bias is None else q_bias.astype(np.float16), g)
+
+
+def oracle_y_dense16(bW, alpha, q_bias, g, x):
+    """Host result through lutGEMM::dequantize_cpu (dense W rounded to fp16) plus the offset term."""
     return oracle.bcq_matmul_ref(x, bW, alpha.astype(np.float16), None if q_bias is None else q_bias.astype(np.float16), g)
 
 
@@ -60,7 +66,10 @@ def test_small_shapes_all_planes(q, N, K, g):
                                         signed_alpha=True, alpha_std=0.05)
         x = synth.activations(1, K, seed=N + K)
         ref = oracle_y(bW, alpha, qb, g, x)
-        check(run_matmul(bW, alpha, qb, g, x), ref, K, f"fp16 N={N} K={K} q={q} bias={bias}")
+        y16 = run_matmul(bW, alpha, qb, g, x)
+        check(y16, ref, K, f"fp16 N={N} K={K} q={q} bias={bias}")
+        rel16, _ = error_metrics(y16, oracle_y_dense16(bW, alpha, qb, g, x), floor=REF16_FLOOR)
+        assert rel16 <= MAX_REL, (N, K, q, bias, rel16)
         check(run_matmul(bW, alpha, qb, g, x, f32=True), ref, K, f"fp32 N={N} K={K} q={q} bias={bias}", fp32_out=True)
 
 
@@ -69,7 +78,10 @@ def test_config1_4096_q3_g128():
     bW, alpha, _ = synth.bcq_layer(N, K, 3, 128, seed=synth.seed_for("cfg1", N, K, 3))
     x = synth.activations(1, K, seed=1)
     ref = oracle_y(bW, alpha, None, 128, x)
-    rel, mae = check(run_matmul(bW, alpha, None, 128, x), ref, K, "config1")
+    y16 = run_matmul(bW, alpha, None, 128, x)
+    rel, mae = check(y16, ref, K, "config1")
+    rel16, mae16 = error_metrics(y16, oracle_y_dense16(bW, alpha, None, 128, x), floor=REF16_FLOOR)
+    assert rel16 <= MAX_REL and mae16 <= MAE
     f64 = oracle.bcq_matmul_f64(x, bW, alpha.astype(np.float16), None, 128)
     rel64, mae64 = error_metrics(run_matmul(bW, alpha, None, 128, x, f32=True), f64)
     assert rel64 < 1e-4 and mae64 < 1e-5      # the fp32 result is essentially exact
@@ -92,6 +104,9 @@ def _sampled_columns_check(N, K, q, g, bias, tag, n_cols=192, uniform=False):
                    None if qb is None else np.ascontiguousarray(qb[:, cols]), g, x)
     rel, mae = error_metrics(y16[:, cols], ref)
     rel32, mae32 = error_metrics(y32[:, cols], ref)
+    ref16 = oracle_y_dense16(np.ascontiguousarray(bW[:, :, cols]), np.ascontiguousarray(alpha[:, :, cols]),
+                             None if qb is None else np.ascontiguousarray(qb[:, cols]), g, x)
+    assert error_metrics(y32[:, cols], ref16, floor=REF16_FLOOR)[0] <= MAX_REL, tag
     assert rel <= MAX_REL and rel32 <= MAX_REL, (tag, rel, rel32)
     assert mae32 <= MAE, (tag, mae32)
     if K <= 12288:

@@ -109,6 +109,11 @@ def test_matmul_ref_vs_f64_and_numpy(N, K, q, g, bias):
         gs = x.astype(np.float32).reshape(2, K // g, g).sum(-1)
         y_parts = y_parts + gs @ qb
     np.testing.assert_allclose(y_ref, y_parts, rtol=1e-5, atol=1e-5)
+    # the fp32 test-side path, composed from its separately restated pieces
+    W32 = oracle.dequantize_from_qw(bW, a_h.astype(np.float32), None if qb is None else qb_h.astype(np.float32), g)
+    y32 = oracle.bcq_matmul_fp32(x, bW, a_h, qb_h, g)
+    assert np.array_equal(y32, oracle.matmul_cpu(x.astype(np.float32), W32))
+    assert np.abs(y32 - y_np).max() <= 1e-5 * scale + 1e-6
 
 
 def test_thread_count_control():
