@@ -145,6 +145,14 @@ int lutgemm_last_cuda_error(void);
 unsigned long long lutgemm_kernel_launch_count(void);
 /* Tuning knob: columns per CTA of the LUT matvec (0 = automatic).  Process-wide. */
 int lutgemm_set_gemv_ntile(int columns);
+/* Tuning knob: 0 = bulk-copy (TMA) fed matvec kernel (default), 1 = register-streaming kernel.
+ * Process-wide; both compute the same function. */
+int lutgemm_set_gemv_variant(int variant);
+/* Synchronises with the device and reads the container's kernel status word: 0 = every kernel
+ * that used this container ran to completion; non-zero = a bounded in-kernel wait ran out
+ * (1 producer, 2 consumer) and the affected output is invalid.  The reference has no error
+ * reporting of any kind (all its entry points return void). */
+int lutgemm_weight_device_status(lutgemm_weight_t w, int* status);
 
 #ifdef __cplusplus
 }

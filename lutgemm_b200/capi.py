@@ -19,6 +19,7 @@ SYMBOLS = (
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
+    "lutgemm_set_gemv_variant", "lutgemm_weight_device_status",
 )
 
 
@@ -73,6 +74,8 @@ def lib():
     L.lutgemm_last_cuda_error.restype = ip
     L.lutgemm_kernel_launch_count.restype = C.c_ulonglong
     L.lutgemm_set_gemv_ntile.argtypes = [ip]
+    L.lutgemm_set_gemv_variant.argtypes = [ip]
+    L.lutgemm_weight_device_status.argtypes = [vp, C.POINTER(ip)]
     for name in SYMBOLS:
         fn = getattr(L, name)
         if name not in ("lutgemm_status_string", "lutgemm_kernel_launch_count"):

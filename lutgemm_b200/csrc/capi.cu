@@ -14,6 +14,7 @@
 
 #include "aux_kernels.cuh"
 #include "gemv_lut.cuh"
+#include "gemv_tma.cuh"
 
 struct lutgemm_weight {
     uint32_t* bW = nullptr;
@@ -26,6 +27,7 @@ struct lutgemm_weight {
     // split-k workspace: partial sums [ceil(K/512)][N] fp32 and per-tile arrival counters
     float* partial = nullptr;
     unsigned* counters = nullptr;
+    int* status = nullptr;     // device word set by a kernel whose bounded wait ran out
     // staging for lutgemm_matmul_host
     void* h_stage_in = nullptr;
     void* d_stage_in = nullptr;
@@ -38,6 +40,7 @@ namespace {
 thread_local int g_last_cuda = 0;
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_ntile_override{0};
+std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
 
@@ -67,6 +70,8 @@ int alloc_workspace(lutgemm_weight* w) {
     LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
     LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
+    LG_CUDA(cudaMalloc(&w->status, sizeof(int)));
+    LG_CUDA(cudaMemset(w->status, 0, sizeof(int)));
     return LUTGEMM_OK;
 }
 
@@ -80,23 +85,39 @@ int sm_count() {
     return sms;
 }
 
-// Columns per CTA: enough CTAs to occupy every SM twice over, but wide enough that building the
-// 64 KB table stays a small part of a CTA's work.
-int choose_ntile(int N, int nslabs) {
+// Columns per CTA: enough CTAs to occupy every SM (`per_sm` CTAs each), but wide enough that
+// building the table stays a small part of a CTA's work.  Rounded to `quantum` columns.
+int choose_ntile(int N, int nslabs, int per_sm, int quantum) {
     int forced = g_ntile_override.load();
     int ntile;
     if (forced > 0) {
         ntile = forced;
     } else {
-        const int slots = 2 * sm_count();
+        const int slots = per_sm * sm_count();
         int tiles = slots / nslabs;
         if (tiles < 1) tiles = 1;
         ntile = (N + tiles - 1) / tiles;
         if (ntile < 512) ntile = 512;
     }
-    ntile = (ntile + lg::kCtaCols - 1) / lg::kCtaCols * lg::kCtaCols;
+    ntile = (ntile + quantum - 1) / quantum * quantum;
     while ((N + ntile - 1) / ntile > kMaxCounters) ntile *= 2;
     return ntile;
+}
+
+template <int WPG>
+int launch_gemv_tma(const lg::Gemv2Params& p, dim3 grid, bool bias, cudaStream_t st) {
+    static bool configured[64][2] = {};   // the attribute is per device
+    auto kern = bias ? lg::gemv_tma_kernel<WPG, true> : lg::gemv_tma_kernel<WPG, false>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev][bias]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kGemv2Smem));
+        if (dev < 64) configured[dev][bias] = true;
+    }
+    kern<<<grid, lg::kGemv2Threads, lg::kGemv2Smem, st>>>(p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
 }
 
 template <int Q>
@@ -117,7 +138,7 @@ int launch_gemv_q(const lg::GemvParams& p, dim3 grid, bool bias, cudaStream_t st
 
 // One matvec row: y (fp16 and/or fp32) = x . W
 int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
-    const bool fast = (w->N % 4 == 0) && (w->K % 256 == 0);
+    const bool fast = (w->N % 4 == 0) && (g_variant.load() == 0 || w->K % 256 == 0);
     if (!fast) {
         dim3 grid((w->N + 127) / 128);
         lg::gemv_generic_kernel<<<grid, 128, 0, st>>>(w->bW, w->alpha, w->q_bias, x, y16, y32, w->N, w->K, w->q, w->g);
@@ -125,12 +146,25 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
         LG_CUDA(cudaGetLastError());
         return LUTGEMM_OK;
     }
+    if (g_variant.load() == 0) {
+        lg::Gemv2Params p2;
+        p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
+        p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
+        p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
+        p2.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
+        p2.n_tile = choose_ntile(w->N, p2.nslabs, 1, lg::kStageCols);
+        dim3 grid2((w->N + p2.n_tile - 1) / p2.n_tile, p2.nslabs);
+        const bool bias2 = w->q_bias != nullptr;
+        if (w->g % 128 == 0) return launch_gemv_tma<4>(p2, grid2, bias2, st);
+        if (w->g % 64 == 0) return launch_gemv_tma<2>(p2, grid2, bias2, st);
+        return launch_gemv_tma<1>(p2, grid2, bias2, st);
+    }
     lg::GemvParams p;
     p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
     p.partial = w->partial; p.counters = w->counters; p.y16 = y16; p.y32 = y32;
     p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
     p.nslabs = (w->K + lg::kSlabK - 1) / lg::kSlabK;
-    p.n_tile = choose_ntile(w->N, p.nslabs);
+    p.n_tile = choose_ntile(w->N, p.nslabs, 2, lg::kCtaCols);
     dim3 grid((w->N + p.n_tile - 1) / p.n_tile, p.nslabs);
     const bool bias = w->q_bias != nullptr;
     switch (w->q) {
@@ -253,6 +287,7 @@ int lutgemm_weight_destroy(lutgemm_weight_t w) {
     }
     if (w->partial) cudaFree(w->partial);
     if (w->counters) cudaFree(w->counters);
+    if (w->status) cudaFree(w->status);
     if (w->h_stage_in) cudaFreeHost(w->h_stage_in);
     if (w->d_stage_in) cudaFree(w->d_stage_in);
     if (w->d_stage_out) cudaFree(w->d_stage_out);
@@ -446,6 +481,18 @@ const char* lutgemm_status_string(int s) {
         case LUTGEMM_ERR_ALIGN: return "pointer or row pitch not 16-byte aligned";
     }
     return "unknown status";
+}
+
+int lutgemm_weight_device_status(lutgemm_weight_t w, int* status) {
+    if (!w || !status) return LUTGEMM_ERR_NULL;
+    LG_CUDA(cudaMemcpy(status, w->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_set_gemv_variant(int variant) {
+    if (variant < 0 || variant > 1) return LUTGEMM_ERR_SHAPE;
+    g_variant.store(variant);
+    return LUTGEMM_OK;
 }
 
 int lutgemm_last_cuda_error(void) { return g_last_cuda; }

@@ -33,9 +33,21 @@ def run_matmul(bW, alpha, q_bias, g, x, f32=False):
         out = torch.empty((m, N), dtype=torch.float16, device="cuda")
         L.matmul(out, xd, w, m)
     torch.cuda.synchronize()
+    import ctypes
+    st = ctypes.c_int(-1)
+    capi.check(capi.lib().lutgemm_weight_device_status(w.handle, ctypes.byref(st)), "device_status")
+    assert st.value == 0, f"kernel status {st.value}"
     y = out.float().cpu().numpy()
     w.close()
     return y
+
+
+@pytest.fixture(params=[0, 1], ids=["bulkcopy", "regstream"])
+def gemv_variant(request):
+    """Both matvec kernels compute the same function; run the shape grid through each."""
+    capi.check(capi.lib().lutgemm_set_gemv_variant(request.param), "set_gemv_variant")
+    yield request.param
+    capi.lib().lutgemm_set_gemv_variant(0)
 
 
 def oracle_y(bW, alpha, q_bias, g, x):
@@ -59,11 +71,12 @@ def check(y, ref, K, what, fp32_out=False):
 # ---- exhaustive small shapes: every q, odd column counts (generic kernel), table kernel with tails
 @pytest.mark.parametrize("q", list(range(1, 9)))
 @pytest.mark.parametrize("N,K,g", [(2, 32, 32), (6, 64, 32), (10, 96, 32), (33, 128, 64), (64, 256, 128),
-                                   (132, 768, 128), (128, 512, 32), (260, 1280, 256), (20, 256, 64)])
-def test_small_shapes_all_planes(q, N, K, g):
+                                   (132, 768, 128), (128, 512, 32), (260, 1280, 256), (20, 256, 64),
+                                   (516, 2048, 64), (12, 96, 96), (1028, 1152, 192), (300, 3072, 1024)])
+def test_small_shapes_all_planes(q, N, K, g, gemv_variant):
     for bias in (False, True):
         bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=synth.seed_for("small", N, K, q, bias), with_bias=bias,
-                                        signed_alpha=True, alpha_std=0.05)
+                                        signed_alpha=True, alpha_std=0.02)
         x = synth.activations(1, K, seed=N + K)
         ref = oracle_y(bW, alpha, qb, g, x)
         y16 = run_matmul(bW, alpha, qb, g, x)
