@@ -54,6 +54,7 @@ def parse():
     ap.add_argument("--rot", type=int, default=8, help="distinct weight sets cycled per step")
     ap.add_argument("--ntile", type=int, default=0, help="columns per CTA of the matvec (0 = automatic)")
     ap.add_argument("--variant", type=int, default=0, help="0 = bulk-copy fed matvec kernel, 1 = register-streaming kernel")
+    ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every matvec from Python instead of replaying a CUDA graph")
@@ -201,6 +202,7 @@ def run_ours(a):
     if a.ntile:
         lib.lutgemm_set_gemv_ntile(a.ntile)
     lib.lutgemm_set_gemv_variant(a.variant)
+    lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
     kernel_name = "gemv_tma_kernel" if a.variant == 0 else "gemv_lut_kernel"
 
     B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)

@@ -148,6 +148,9 @@ int lutgemm_set_gemv_ntile(int columns);
 /* Tuning knob: 0 = bulk-copy (TMA) fed matvec kernel (default), 1 = register-streaming kernel.
  * Process-wide; both compute the same function. */
 int lutgemm_set_gemv_variant(int variant);
+/* Tuning knob: 1 (default) launches the TMA-fed matvec with programmatic stream serialization, so
+ * that its weight stream starts while the previous kernel of the stream drains; 0 = plain launches. */
+int lutgemm_set_dependent_launch(int enabled);
 /* Synchronises with the device and reads the container's kernel status word: 0 = every kernel
  * that used this container ran to completion; non-zero = a bounded in-kernel wait ran out
  * (1 producer, 2 consumer) and the affected output is invalid.  The reference has no error

@@ -9,6 +9,7 @@
 #include <new>
 #include <vector>
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -28,6 +29,10 @@ struct lutgemm_weight {
     float* partial = nullptr;
     unsigned* counters = nullptr;
     int* status = nullptr;     // device word set by a kernel whose bounded wait ran out
+    // TMA descriptors of the packed planes and of alpha (valid when tma_ok)
+    CUtensorMap tmW, tmA;
+    bool tma_ok = false;
+    int a_rows = 1;            // alpha groups per 512-k slab
     // staging for lutgemm_matmul_host
     void* h_stage_in = nullptr;
     void* d_stage_in = nullptr;
@@ -40,6 +45,7 @@ namespace {
 thread_local int g_last_cuda = 0;
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_ntile_override{0};
+std::atomic<int> g_pdl{1};
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
@@ -65,8 +71,58 @@ int check_shape(int row, int col, int q, int is_row_wise, int groups, int* N, in
     return LUTGEMM_OK;
 }
 
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library does not link libcuda
+// (and therefore still loads on a machine without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// Descriptors for the TMA-fed matvec: planes as {N, q, K/32} uint32 with box {256, 1, 16}; alpha as
+// {N, q, G} fp16 with box {256, 1, groups per 512-k slab}.  Leaves tma_ok false when the shape does
+// not qualify (N % 8, group size neither dividing nor a multiple of 512) or the driver refuses.
+void make_tensor_maps(lutgemm_weight* w) {
+    w->tma_ok = false;
+    const int g = w->g;
+    if (w->N % 8 != 0 || !((lg::kSlab2 % g == 0) || (g % lg::kSlab2 == 0))) return;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return;
+    w->a_rows = (g >= lg::kSlab2) ? 1 : lg::kSlab2 / g;
+    const cuuint64_t N = (cuuint64_t)w->N, q = (cuuint64_t)w->q;
+    {
+        cuuint64_t dims[3] = {N, q, (cuuint64_t)(w->K / 32)};
+        cuuint64_t strides[2] = {N * 4, q * N * 4};
+        cuuint32_t box[3] = {(cuuint32_t)lg::kStageCols, 1, (cuuint32_t)lg::kSlabWords};
+        cuuint32_t es[3] = {1, 1, 1};
+        if (enc(&w->tmW, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w->bW, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return;
+    }
+    {
+        cuuint64_t dims[3] = {N, q, (cuuint64_t)w->G};
+        cuuint64_t strides[2] = {N * 2, q * N * 2};
+        cuuint32_t box[3] = {(cuuint32_t)lg::kStageCols, 1, (cuuint32_t)w->a_rows};
+        cuuint32_t es[3] = {1, 1, 1};
+        if (enc(&w->tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, w->alpha, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return;
+    }
+    w->tma_ok = true;
+}
+
 int alloc_workspace(lutgemm_weight* w) {
-    const size_t nslabs = (size_t)(w->K + lg::kSlabK - 1) / lg::kSlabK;
+    make_tensor_maps(w);
+    const size_t nslabs = (size_t)(w->K + lg::kSlab2 - 1) / lg::kSlab2;
     LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
     LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
@@ -105,16 +161,28 @@ int choose_ntile(int N, int nslabs, int per_sm, int quantum) {
 }
 
 template <int WPG>
-int launch_gemv_tma(const lg::Gemv2Params& p, dim3 grid, bool bias, cudaStream_t st) {
+int launch_gemv_tma(const lutgemm_weight* w, const lg::Gemv2Params& p, dim3 grid, bool bias, cudaStream_t st) {
     static bool configured[64][2] = {};   // the attribute is per device
     auto kern = bias ? lg::gemv_tma_kernel<WPG, true> : lg::gemv_tma_kernel<WPG, false>;
     int dev = 0;
     LG_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev][bias]) {
-        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kGemv2Smem));
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kSmemLimit));
         if (dev < 64) configured[dev][bias] = true;
     }
-    kern<<<grid, lg::kGemv2Threads, lg::kGemv2Smem, st>>>(p);
+    // Programmatic stream serialization: the kernel may begin (and start its weight stream) while the
+    // previous kernel in the stream drains; it orders itself with griddepcontrol.wait.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(lg::kGemv2Threads);
+    cfg.dynamicSmemBytes = (size_t)lg::gemv2_smem_bytes(p.a_rows);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    LG_CUDA(cudaLaunchKernelEx(&cfg, kern, w->tmW, w->tmA, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;
@@ -138,7 +206,8 @@ int launch_gemv_q(const lg::GemvParams& p, dim3 grid, bool bias, cudaStream_t st
 
 // One matvec row: y (fp16 and/or fp32) = x . W
 int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
-    const bool fast = (w->N % 4 == 0) && (g_variant.load() == 0 || w->K % 256 == 0);
+    const bool use_tma = (g_variant.load() == 0) && w->tma_ok;
+    const bool fast = use_tma || ((w->N % 4 == 0) && (w->K % 256 == 0));
     if (!fast) {
         dim3 grid((w->N + 127) / 128);
         lg::gemv_generic_kernel<<<grid, 128, 0, st>>>(w->bW, w->alpha, w->q_bias, x, y16, y32, w->N, w->K, w->q, w->g);
@@ -146,18 +215,18 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
         LG_CUDA(cudaGetLastError());
         return LUTGEMM_OK;
     }
-    if (g_variant.load() == 0) {
+    if (use_tma) {
         lg::Gemv2Params p2;
         p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
         p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
         p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
         p2.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
+        p2.a_rows = w->a_rows;
         p2.n_tile = choose_ntile(w->N, p2.nslabs, 1, lg::kStageCols);
         dim3 grid2((w->N + p2.n_tile - 1) / p2.n_tile, p2.nslabs);
         const bool bias2 = w->q_bias != nullptr;
-        if (w->g % 128 == 0) return launch_gemv_tma<4>(p2, grid2, bias2, st);
-        if (w->g % 64 == 0) return launch_gemv_tma<2>(p2, grid2, bias2, st);
-        return launch_gemv_tma<1>(p2, grid2, bias2, st);
+        if (w->g % 128 == 0) return launch_gemv_tma<2>(w, p2, grid2, bias2, st);
+        return launch_gemv_tma<1>(w, p2, grid2, bias2, st);
     }
     lg::GemvParams p;
     p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
@@ -492,6 +561,11 @@ int lutgemm_weight_device_status(lutgemm_weight_t w, int* status) {
 int lutgemm_set_gemv_variant(int variant) {
     if (variant < 0 || variant > 1) return LUTGEMM_ERR_SHAPE;
     g_variant.store(variant);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_set_dependent_launch(int enabled) {
+    g_pdl.store(enabled ? 1 : 0);
     return LUTGEMM_OK;
 }
 

@@ -1,33 +1,41 @@
-// LUT matvec for BCQ weights (m = 1), sm_100a: bulk-copy (TMA) fed, one CTA per SM.
+// LUT matvec for BCQ weights (m = 1), sm_100a: TMA fed, one CTA per SM.
 //
 // Replaces _nqmv / _nqmv_bias of the reference (lutGEMM/src/cuda/kernels/mv_fp16.hpp:25-97,
 // lutGEMM/src/cuda/kernels/mv_fp16_bias.hpp:24-118).  Same mathematics — a 2^8-entry table of signed
 // partial sums per 8 activations, one lookup per packed weight byte — mapped to the machine as follows.
 //
-//  CTA = (column tile) x (1024-k slab).  544 threads: 16 consumer warps + 1 producer warp.
+//  CTA = (column tile) x (512-k slab).  544 threads: 16 consumer warps + 1 producer warp.
 //
-//  Table.  lut[idx][slot] fp32, TRANSPOSED: the shared-memory bank is chosen by the slot (the
-//  8-activation chunk), not by the random weight byte.  128 chunks -> two [256][64] halves of 64 KB.
-//  Chunk (word kw = 4a + j, byte beta) lives in slot 32 j + 4 a + beta.  In every lookup instruction
-//  the 32 lanes of a warp hold 8 different a and, through a per-quad byte rotation, 4 different beta:
-//  32 different banks, so lookups never conflict, whatever the weights are.  One PRMT turns a packed
-//  byte into the shared-memory offset (idx << 8 | slot * 4): a lookup is PRMT + LDS + add.
+//  Table (64 KB).  lut[idx][slot] fp32, TRANSPOSED: the shared-memory bank is chosen by the slot (the
+//  8-activation chunk), not by the random weight byte.  The slab's 16 packed k-words are numbered
+//  kw = 4 G + jp + 2 u (G = 0..3: a run of four words = 128 k; jp, u = 0..1); chunk (kw, byte beta)
+//  lives in slot 32 u + 8 G + 4 jp + beta.  In every lookup instruction the 32 lanes of a warp hold
+//  the 8 different (G, jp) and, through a per-lane byte rotation, 4 different beta: 32 different
+//  banks, so lookups never conflict, whatever the weights are.  One PRMT turns a packed byte into the
+//  shared-memory offset (idx << 8 | slot * 4): a lookup is PRMT + LDS + add.
 //
-//  Weights.  The producer warp streams the packed planes with plain bulk copies (cp.async.bulk,
-//  global -> shared, mbarrier completion; no multicast): one stage = one bit plane x 1024 k x 256
-//  columns = 32 rows of 1 KB, each row one copy, rows padded to 1040 B so that the consumers'
-//  128-bit reads (8 lanes = 8 different k-words per quarter warp) touch 8 different bank groups.
-//  Three stages (100 KB) are in flight; a consumer warp releases a stage as soon as its 4 words per
-//  lane are in registers.
+//  Weights and scales.  One producer lane issues, per stage, one tiled TMA load of the box
+//  [16 k-words][1 plane][256 columns] of the packed planes (16 KB, dense rows of 1 KB) and one of the
+//  box [groups of the slab][1 plane][256 columns] of alpha; completion is counted on an mbarrier, no
+//  multicast.  Up to 8 stages (>= 100 KB) are in flight, which is what it takes to keep HBM busy from
+//  one CTA per SM; a consumer warp releases a stage as soon as its words are in registers.  Lane
+//  (c8 = lane & 7, rr = lane >> 3) of warp (cb = warp & 7, h = warp >> 3) reads columns
+//  32 cb + 4 c8 .. +3 of rows 4 rr + ((c8 & 1) ^ h) + 2 u: a quarter warp reads eight consecutive
+//  16-byte chunks, which is conflict free on dense rows.
 //
-//  Scales.  A lane's four words of a slab are consecutive in k, so with group size >= 128 they share
-//  one alpha: 16 lookups are summed, then one FMA (WPG = words per group = 4; 2 and 1 for group
-//  sizes 64 and 32).  alpha / q_bias come through ordinary 64-bit loads, issued before the stage wait.
+//  Scales.  A lane's two words of a stage lie in one 128-k run, so with group size % 128 == 0 they
+//  share one alpha: 8 lookups are summed, then one FMA (WPG = 2); otherwise one FMA per word.
 //
-//  Result.  fp32 throughout; the 8 lanes that share columns are added with shuffles, each CTA writes
-//  its slab's partial sums, and the last CTA of a column tile adds the slabs in slab order and rounds
-//  to fp16 once: no atomics on data, no memset, run-to-run identical results.
+//  Result.  fp32 throughout; the 4 lanes that share columns are added with shuffles, the two warp
+//  halves are added through shared memory, each CTA writes its slab's partial sums, and the last CTA
+//  of a column tile adds the slabs in slab order and rounds to fp16 once: no atomics on data, no
+//  memset, run-to-run identical results.
+//
+//  Launch.  The kernel is launched with programmatic stream serialization: its weight stream starts
+//  while the previous kernel in the stream drains; everything a predecessor may have produced (the
+//  activations) or may still use (workspace, output) is touched only after griddepcontrol.wait.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -36,16 +44,29 @@
 
 namespace lg {
 
-constexpr int kSlab2 = 1024;                                // k per CTA
+constexpr int kSlab2 = 512;                                 // k per CTA
+constexpr int kSlabWords = kSlab2 / 32;                     // 16 packed k-words per slab
 constexpr int kStageCols = 256;                             // columns per stage
 constexpr int kConsWarps = 16;
 constexpr int kGemv2Threads = (kConsWarps + 1) * 32;        // 544
-constexpr int kStages = 3;
-constexpr int kRowPitch = kStageCols * 4 + 16;              // 1040
-constexpr int kStageBytes = 32 * kRowPitch;                 // 33280
-constexpr int kLut2Bytes = 2 * 65536;
-constexpr int kBarOff = kLut2Bytes + kStages * kStageBytes; // 230912
-constexpr int kGemv2Smem = kBarOff + 64;
+constexpr int kMaxStages = 8;
+constexpr int kRowPitch = kStageCols * 4;                   // 1024: dense TMA box rows
+constexpr int kWStageBytes = kSlabWords * kRowPitch;        // 16384
+constexpr int kARowPitch = kStageCols * 2;                  // 512: one alpha group row of the box
+constexpr int kLut2Bytes = 65536;
+constexpr int kSmemLimit = 232448;                          // 227 KB opt-in maximum per CTA
+// shared memory: table | half-warp exchange (1 KB) | barriers | stages (weight box + alpha box each)
+constexpr int kXchgOff = kLut2Bytes;
+constexpr int kBarOff = kXchgOff + 1024;
+constexpr int kStage0Off = kBarOff + 256;
+__host__ __device__ constexpr int gemv2_stage_bytes(int a_rows) { return kWStageBytes + a_rows * kARowPitch; }
+__host__ __device__ constexpr int gemv2_num_stages(int a_rows) {
+    return (kSmemLimit - kStage0Off) / gemv2_stage_bytes(a_rows) < kMaxStages
+               ? (kSmemLimit - kStage0Off) / gemv2_stage_bytes(a_rows) : kMaxStages;
+}
+__host__ __device__ constexpr int gemv2_smem_bytes(int a_rows) {
+    return kStage0Off + gemv2_num_stages(a_rows) * gemv2_stage_bytes(a_rows);
+}
 
 enum { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusConsumerTimeout = 2 };
 
@@ -54,7 +75,7 @@ struct Gemv2Params {
     const __half* alpha;     // [G][q][N]
     const __half* q_bias;    // [G][N] or nullptr
     const __half* x;         // [K]
-    float* partial;          // [nslabs][N] split-k workspace (unused when nslabs == 1)
+    float* partial;          // [nslabs][N] split-k workspace
     unsigned* counters;      // [gridDim.x], zero between launches
     int* status;             // device word; set non-zero if a bounded wait ran out
     __half* y16;             // [N] or nullptr
@@ -62,6 +83,7 @@ struct Gemv2Params {
     int N, K, q, g;
     int n_tile;              // columns per CTA, multiple of kStageCols
     int nslabs;              // gridDim.y
+    int a_rows;              // alpha groups per slab (rows of the alpha box): max(1, 512 / g)
 };
 
 __device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
@@ -89,9 +111,13 @@ __device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
         : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
     return d;
 }
+// Programmatic dependent launch: let the next kernel in the stream start launching / wait for the
+// previous one to finish and flush.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Sum of the four table entries selected by the four bytes of one packed word.  IMM is the
-// compile-time part of the slot address (table half and word parity).
+// compile-time part of the slot address (which of the lane's two words).
 template <int IMM>
 __device__ __forceinline__ float2 lookup_word(const unsigned char* lut, uint32_t word, uint32_t cs,
                                               const uint32_t (&sel)[4]) {
@@ -102,13 +128,13 @@ __device__ __forceinline__ float2 lookup_word(const unsigned char* lut, uint32_t
     return add_f32x2(make_float2(l0, l1), make_float2(l2, l3));
 }
 
-// Table for the 128 chunks of one slab.  Consumer thread t owns slot (t & 127) and the 64 entries
-// idx in [64 (t >> 7), +64), walked in Gray-code order (one add per entry).  A warp stores 32
+// Table for the 64 chunks of one slab.  Consumer thread t owns slot (t & 63) and the 32 entries
+// idx in [32 (t >> 6), +32), walked in Gray-code order (one add per entry).  A warp stores 32
 // consecutive slots of one idx row: conflict free.
 __device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, int k0, int K, int ctid) {
-    const int slot = ctid & 127, part = ctid >> 7;
-    const int j = slot >> 5, a = (slot & 31) >> 2, beta = slot & 3;
-    const int chunk = 4 * (4 * a + j) + beta;            // 8-activation chunk in natural k order
+    const int slot = ctid & 63, part = ctid >> 6;
+    const int u = slot >> 5, G = (slot >> 3) & 3, jp = (slot >> 2) & 1, beta = slot & 3;
+    const int chunk = 4 * (4 * G + jp + 2 * u) + beta;       // 8-activation chunk in natural k order
     float xv[8];
     {
         uint4 raw = make_uint4(0, 0, 0, 0);
@@ -117,14 +143,15 @@ __device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, 
         const float2 f2 = half2_bits_to_float2(raw.z), f3 = half2_bits_to_float2(raw.w);
         xv[0] = f0.x; xv[1] = f0.y; xv[2] = f1.x; xv[3] = f1.y; xv[4] = f2.x; xv[5] = f2.y; xv[6] = f3.x; xv[7] = f3.y;
     }
-    float e = -xv[0] - xv[1] - xv[2] - xv[3] - xv[4] - xv[5];
-    e += (part & 1) ? xv[6] : -xv[6];
-    e += (part & 2) ? xv[7] : -xv[7];
-    unsigned char* base = lut + (slot >> 6) * 65536 + part * (64 * 256) + (slot & 63) * 4;
+    float e = -xv[0] - xv[1] - xv[2] - xv[3] - xv[4];
+    e += (part & 1) ? xv[5] : -xv[5];
+    e += (part & 2) ? xv[6] : -xv[6];
+    e += (part & 4) ? xv[7] : -xv[7];
+    unsigned char* base = lut + part * (32 * 256) + slot * 4;
     *reinterpret_cast<float*>(base) = e;
 #pragma unroll
-    for (int c = 1; c < 64; c++) {
-        const int t = (c & 1) ? 0 : (c & 2) ? 1 : (c & 4) ? 2 : (c & 8) ? 3 : (c & 16) ? 4 : 5;   // bit that flips
+    for (int c = 1; c < 32; c++) {
+        const int t = (c & 1) ? 0 : (c & 2) ? 1 : (c & 4) ? 2 : (c & 8) ? 3 : 4;   // bit that flips
         const int gcode = c ^ (c >> 1);
         const float two_x = 2.0f * xv[t];
         e = ((gcode >> t) & 1) ? e + two_x : e - two_x;
@@ -132,24 +159,26 @@ __device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, 
     }
 }
 
-// WPG: packed words per alpha group inside a lane's four consecutive words (4: g >= 128, 2: g = 64,
-// 1: g = 32 or any other multiple of 32).  BIAS: container has q_bias.
+// WPG: packed words per alpha group among a lane's two words of a stage (2: g % 128 == 0, else 1).
+// BIAS: container has q_bias.  tmW: 3-D map {N, q, K/32} of uint32, box {256, 1, 16};
+// tmA: 3-D map {N, q, G} of fp16, box {256, 1, a_rows}.
 template <int WPG, bool BIAS>
 __global__ void __launch_bounds__(kGemv2Threads, 1)
-gemv_tma_kernel(const Gemv2Params p) {
+gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+                const Gemv2Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* lut = smem;
-    const uint32_t stage0 = smem_u32(smem + kLut2Bytes);
-    const uint32_t bar_full = smem_u32(smem + kBarOff);          // kStages x 8 B
-    const uint32_t bar_empty = bar_full + 8 * kStages;
-    int* s_flag = reinterpret_cast<int*>(smem + kBarOff + 48);
+    const int stage_bytes = gemv2_stage_bytes(p.a_rows);
+    const int nstages = gemv2_num_stages(p.a_rows);
+    const uint32_t bar_full = smem_u32(smem + kBarOff);          // nstages x 8 B
+    const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+    int* s_flag = reinterpret_cast<int*>(smem + kBarOff + 16 * kMaxStages);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int N = p.N, q = p.q;
     const int slab = blockIdx.y;
     const int k0 = slab * kSlab2;
-    const int kw0 = slab * (kSlab2 / 32);
-    const int rows_valid = min(32, p.K / 32 - kw0);              // packed words of this slab that exist
+    const int kw0 = slab * kSlabWords;
     const int n_begin = blockIdx.x * p.n_tile;
     const int n_end = min(N, n_begin + p.n_tile);
     const int ncg = (n_end - n_begin + kStageCols - 1) / kStageCols;
@@ -157,60 +186,70 @@ gemv_tma_kernel(const Gemv2Params p) {
     const size_t rowN = (size_t)N;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < nstages; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, kConsWarps);
         }
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
 
     if (warp == kConsWarps) {
-        // ---------------- producer: one row (one packed k-word, 256 columns) per lane ----------------
-        const int a = lane & 7, j = lane >> 3;
-        const int kw_local = 4 * a + j;
-        const bool row_ok = kw_local < rows_valid;
-        const uint32_t* src_row = p.bW + (size_t)(kw0 + kw_local) * q * rowN;
-        for (int t = 0; t < total_stages; t++) {
-            const int cg = t / q, b = t - cg * q, slot = t % kStages;
-            if (t >= kStages) {
-                if (!mbar_wait_bounded(bar_empty + 8 * slot, ((t / kStages) - 1) & 1)) {
-                    if (lane == 0) atomicExch(p.status, kStatusProducerTimeout);
-                    break;
+        // ---------------- producer: one lane, two TMA loads per stage.  Weights and scales are never
+        // written by a kernel, so the stream may start before the previous kernel has finished. -------
+        if (lane == 0) {
+            tma_prefetch_descriptor(&tmW);
+            tma_prefetch_descriptor(&tmA);
+            const int grp0 = k0 / p.g;
+            const uint32_t tx = (uint32_t)stage_bytes;           // out-of-range parts are zero-filled and counted
+            int slot = 0, round = 0;
+            for (int t = 0; t < total_stages; t++) {
+                const int cg = t / q, b = t - cg * q;
+                if (round > 0) {
+                    if (!mbar_wait_bounded(bar_empty + 8 * slot, (round - 1) & 1)) {
+                        atomicExch(p.status, kStatusProducerTimeout);
+                        break;
+                    }
                 }
+                const int col0 = n_begin + cg * kStageCols;
+                const uint32_t dst = smem_u32(smem + kStage0Off + slot * stage_bytes);
+                mbar_arrive_expect_tx(bar_full + 8 * slot, tx);
+                tma_load_3d(dst, &tmW, col0, b, kw0, bar_full + 8 * slot);
+                tma_load_3d(dst + kWStageBytes, &tmA, col0, b, grp0, bar_full + 8 * slot);
+                if (++slot == nstages) { slot = 0; round++; }
             }
-            const int col0 = n_begin + cg * kStageCols;
-            const uint32_t bytes = (uint32_t)min(kStageCols, n_end - col0) * 4u;
-            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * slot, bytes * (uint32_t)rows_valid);
-            __syncwarp();
-            if (row_ok)
-                bulk_g2s(stage0 + slot * kStageBytes + lane * kRowPitch, src_row + (size_t)b * rowN + col0, bytes,
-                         bar_full + 8 * slot);
         }
+        pdl_wait_prior_grids();
     } else {
         // ---------------- consumers ----------------
-        const int a = lane & 7;      // this lane's words in the slab: kw = 4a + j, j = 0..3
-        const int r = lane >> 3;     // column quad inside the warp's 16 columns; also the byte rotation
+        const int c8 = lane & 7;                 // 16-byte column chunk inside the warp's 32 columns
+        const int rr = lane >> 3;                // G: which 128-k run of the slab
+        const int cb = warp & 7, h = warp >> 3;
+        const int jp = (c8 & 1) ^ h;             // this lane's words in the slab: kw = 4 rr + jp + 2 u, u = 0, 1
+        pdl_wait_prior_grids();                  // the activations may come from the previous kernel
         build_lut2(lut, p.x, k0, p.K, tid);
         asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
 
         uint32_t cs = 0, sel[4];
 #pragma unroll
-        for (int b = 0; b < 4; b++) cs |= (uint32_t)(16 * a + 4 * b) << (8 * b);
+        for (int b = 0; b < 4; b++) cs |= (uint32_t)(32 * rr + 16 * jp + 4 * b) << (8 * b);
 #pragma unroll
         for (int s = 0; s < 4; s++) {
-            const uint32_t beta = (uint32_t)(s + r) & 3u;
+            const uint32_t beta = (uint32_t)(s + (c8 >> 1)) & 3u;
             sel[s] = 0xCC00u | (beta << 4) | (4u + beta);     // -> {0, 0, word.byte[beta], cs.byte[beta]}
         }
 
-        constexpr int NG = 4 / WPG;                            // alpha groups among the lane's 4 words
+        constexpr int NG = 2 / WPG;                            // alpha groups among the lane's 2 words
+        int arow[NG];                                          // row of each group in the alpha box
         int grp[NG];
         bool grp_ok[NG];
 #pragma unroll
         for (int gi = 0; gi < NG; gi++) {
-            const int kw_local = 4 * a + gi * WPG;
+            const int kw_local = 4 * rr + jp + 2 * gi * WPG;   // NG == 2: word u = gi; NG == 1: both words
             grp[gi] = (k0 + 32 * kw_local) / p.g;
-            grp_ok[gi] = kw_local < rows_valid;
+            arow[gi] = grp[gi] - k0 / p.g;
+            grp_ok[gi] = (k0 + 32 * kw_local) < p.K;
         }
         float xsum[NG];
         if (BIAS) {
@@ -220,8 +259,8 @@ gemv_tma_kernel(const Gemv2Params p) {
                 float s = 0.f;
 #pragma unroll
                 for (int jj = 0; jj < WPG; jj++) {
-                    const int j = gi * WPG + jj;
-                    const unsigned char* e = lut + (j >> 1) * 65536 + 255 * 256 + ((j & 1) * 32 + 4 * a) * 4;
+                    const int u = gi * WPG + jj;
+                    const unsigned char* e = lut + 255 * 256 + (32 * u + 8 * rr + 4 * jp) * 4;
                     s += *reinterpret_cast<const float*>(e) + *reinterpret_cast<const float*>(e + 4) +
                          *reinterpret_cast<const float*>(e + 8) + *reinterpret_cast<const float*>(e + 12);
                 }
@@ -230,27 +269,13 @@ gemv_tma_kernel(const Gemv2Params p) {
         }
 
         float* part_out = p.partial + (size_t)slab * rowN;
-        const bool direct = (p.nslabs == 1);
-        const uint32_t my_off = (uint32_t)a * kRowPitch + (uint32_t)(16 * warp + 4 * r) * 4u;
+        float4* xchg = reinterpret_cast<float4*>(smem + kXchgOff) + cb * 8 + c8;
+        const int col_in_stage = 32 * cb + 4 * c8;
+        const uint32_t w_off = (uint32_t)(4 * rr + jp) * kRowPitch + (uint32_t)col_in_stage * 4u;
         bool aborted = false;
-        int t = 0;
-        // alpha is fetched two stages ahead of its use (a stage lasts about as long as one trip to L2/HBM)
-        const int col_w = n_begin + 16 * warp + 4 * r;
-        int pf_cg = 0, pf_b = 0;
-        auto fetch_alpha = [&](uint2 (&dst)[NG]) {
-            const int c = col_w + pf_cg * kStageCols;
-            const bool ok = (pf_cg < ncg) && (c < n_end);
-#pragma unroll
-            for (int gi = 0; gi < NG; gi++)
-                dst[gi] = (ok && grp_ok[gi]) ? ldg_nc_v2(p.alpha + ((size_t)grp[gi] * q + pf_b) * rowN + c)
-                                             : make_uint2(0u, 0u);
-            if (++pf_b == q) { pf_b = 0; pf_cg++; }
-        };
-        uint2 av[NG], av1[NG], av2[NG];
-        fetch_alpha(av1);
-        fetch_alpha(av2);
-        for (int cg = 0; cg < ncg && !aborted; cg++) {
-            const int col = n_begin + cg * kStageCols + 16 * warp + 4 * r;
+        int slot = 0, round = 0;
+        for (int cg = 0; cg < ncg; cg++) {
+            const int col = n_begin + cg * kStageCols + col_in_stage;
             const bool col_ok = col < n_end;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             uint2 bv[NG];
@@ -259,37 +284,35 @@ gemv_tma_kernel(const Gemv2Params p) {
                 for (int gi = 0; gi < NG; gi++)
                     bv[gi] = (col_ok && grp_ok[gi]) ? ldg_nc_v2(p.q_bias + (size_t)grp[gi] * rowN + col) : make_uint2(0u, 0u);
             }
-            for (int b = 0; b < q; b++, t++) {
-                const int slot = t % kStages;
-#pragma unroll
-                for (int gi = 0; gi < NG; gi++) { av[gi] = av1[gi]; av1[gi] = av2[gi]; }
-                fetch_alpha(av2);
-                if (!mbar_wait_bounded(bar_full + 8 * slot, (t / kStages) & 1)) {
+            for (int b = 0; b < q && !aborted; b++) {
+                if (!mbar_wait_bounded(bar_full + 8 * slot, round & 1)) {
                     atomicExch(p.status, kStatusConsumerTimeout);
-                    aborted = true;
+                    aborted = true;     // keep walking the loops (the pair barriers below must stay matched)
                     break;
                 }
-                const unsigned char* st = smem + kLut2Bytes + slot * kStageBytes + my_off;
-                uint4 wv[4];
+                const unsigned char* st = smem + kStage0Off + slot * stage_bytes + w_off;
+                const unsigned char* sa = smem + kStage0Off + slot * stage_bytes + kWStageBytes + col_in_stage * 2;
+                uint4 wv[2];
 #pragma unroll
-                for (int j = 0; j < 4; j++) wv[j] = *reinterpret_cast<const uint4*>(st + j * 8 * kRowPitch);
+                for (int u = 0; u < 2; u++) wv[u] = *reinterpret_cast<const uint4*>(st + u * 2 * kRowPitch);
+                uint2 av[NG];
+#pragma unroll
+                for (int gi = 0; gi < NG; gi++) av[gi] = *reinterpret_cast<const uint2*>(sa + arow[gi] * kARowPitch);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * slot);   // words are in registers: free the stage
+                if (++slot == nstages) { slot = 0; round++; }
 
 #pragma unroll
                 for (int gi = 0; gi < NG; gi++) {
                     float2 s2[4];
 #pragma unroll
                     for (int jj = 0; jj < WPG; jj++) {
-                        const int j = gi * WPG + jj;
-                        const uint32_t ww[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+                        const int u = gi * WPG + jj;
+                        const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
-                            float2 v;
-                            if (j == 0) v = lookup_word<0>(lut, ww[c], cs, sel);
-                            else if (j == 1) v = lookup_word<128>(lut, ww[c], cs, sel);
-                            else if (j == 2) v = lookup_word<65536>(lut, ww[c], cs, sel);
-                            else v = lookup_word<65536 + 128>(lut, ww[c], cs, sel);
+                            const float2 v = (u == 0) ? lookup_word<0>(lut, ww[c], cs, sel)
+                                                      : lookup_word<128>(lut, ww[c], cs, sel);
                             s2[c] = (jj == 0) ? v : add_f32x2(s2[c], v);
                         }
                     }
@@ -300,7 +323,6 @@ gemv_tma_kernel(const Gemv2Params p) {
                     acc[3] = fmaf(s2[3].x + s2[3].y, a23.y, acc[3]);
                 }
             }
-            if (aborted) break;
             if (BIAS) {
 #pragma unroll
                 for (int gi = 0; gi < NG; gi++) {
@@ -311,29 +333,23 @@ gemv_tma_kernel(const Gemv2Params p) {
                     acc[3] = fmaf(xsum[gi], b23.y, acc[3]);
                 }
             }
-            // add the 8 lanes (k words) that share a column quad
+            // add the 4 lanes (128-k runs) that share a column quad
 #pragma unroll
-            for (int off = 1; off < 8; off <<= 1) {
+            for (int off = 8; off < 32; off <<= 1) {
 #pragma unroll
                 for (int c = 0; c < 4; c++) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], off);
             }
-            if (a == 0 && col_ok) {
-                if (!direct) {
-                    *reinterpret_cast<float4*>(part_out + col) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                } else {
-                    if (p.y32) *reinterpret_cast<float4*>(p.y32 + col) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                    if (p.y16) {
-                        __half2 lo = __floats2half2_rn(acc[0], acc[1]), hi = __floats2half2_rn(acc[2], acc[3]);
-                        uint2 o;
-                        o.x = *reinterpret_cast<uint32_t*>(&lo);
-                        o.y = *reinterpret_cast<uint32_t*>(&hi);
-                        *reinterpret_cast<uint2*>(p.y16 + col) = o;
-                    }
-                }
+            // add the two warp halves (the other word parity) through shared memory
+            if (h == 1 && rr == 0) *xchg = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + cb) : "memory");
+            if (h == 0 && rr == 0 && col_ok) {
+                const float4 o = *xchg;
+                *reinterpret_cast<float4*>(part_out + col) =
+                    make_float4(acc[0] + o.x, acc[1] + o.y, acc[2] + o.z, acc[3] + o.w);
             }
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + cb) : "memory");   // exchange slot free for the next column group
         }
     }
-    if (p.nslabs == 1) return;
 
     // Split-k finish: the last CTA of this column tile adds the slabs in slab order.
     __threadfence();
@@ -348,8 +364,15 @@ gemv_tma_kernel(const Gemv2Params p) {
     for (int c = n_begin + 4 * tid; c < n_end; c += 4 * kGemv2Threads) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = p.partial + c;
-#pragma unroll 4
-        for (int sl = 0; sl < p.nslabs; sl++) {
+        int sl = 0;
+        for (; sl + 8 <= p.nslabs; sl += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sl + i) * rowN));
+#pragma unroll
+            for (int i = 0; i < 8; i++) { s.x += v[i].x; s.y += v[i].y; s.z += v[i].z; s.w += v[i].w; }
+        }
+        for (; sl < p.nslabs; sl++) {
             const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sl * rowN));
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
