@@ -148,6 +148,12 @@ int lutgemm_set_gemv_ntile(int columns);
 /* Tuning knob: 0 = bulk-copy (TMA) fed matvec kernel (default), 1 = register-streaming kernel.
  * Process-wide; both compute the same function. */
 int lutgemm_set_gemv_variant(int variant);
+/* 0 (default): the TMA-fed matvec adds its k-slabs with fp32 reductions in L2, whose order is not
+ * fixed (results agree to fp32 rounding of a 24-term sum, then one fp16 rounding).  1: one partial
+ * row per slab, added in slab order: bit-reproducible run to run, about 10 % slower.  Switch only
+ * while no matvec is in flight.  (The reference's half2 atomicAdd accumulation,
+ * lutGEMM/src/cuda/kernels/mv_fp16.hpp:95, has no ordered mode.) */
+int lutgemm_set_ordered_reduction(int enabled);
 /* Tuning knob: 1 (default) launches the TMA-fed matvec with programmatic stream serialization, so
  * that its weight stream starts while the previous kernel of the stream drains; 0 = plain launches. */
 int lutgemm_set_dependent_launch(int enabled);

@@ -46,6 +46,7 @@ thread_local int g_last_cuda = 0;
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_ntile_override{0};
 std::atomic<int> g_pdl{1};
+std::atomic<int> g_ordered{0};
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
@@ -124,6 +125,7 @@ int alloc_workspace(lutgemm_weight* w) {
     make_tensor_maps(w);
     const size_t nslabs = (size_t)(w->K + lg::kSlab2 - 1) / lg::kSlab2;
     LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
+    LG_CUDA(cudaMemset(w->partial, 0, nslabs * (size_t)w->N * sizeof(float)));   // row 0 doubles as the reduction row
     LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMalloc(&w->status, sizeof(int)));
@@ -222,6 +224,7 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
         p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
         p2.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
         p2.a_rows = w->a_rows;
+        p2.ordered = g_ordered.load();
         p2.n_tile = choose_ntile(w->N, p2.nslabs, 1, lg::kStageCols);
         dim3 grid2((w->N + p2.n_tile - 1) / p2.n_tile, p2.nslabs);
         const bool bias2 = w->q_bias != nullptr;
@@ -561,6 +564,11 @@ int lutgemm_weight_device_status(lutgemm_weight_t w, int* status) {
 int lutgemm_set_gemv_variant(int variant) {
     if (variant < 0 || variant > 1) return LUTGEMM_ERR_SHAPE;
     g_variant.store(variant);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_set_ordered_reduction(int enabled) {
+    g_ordered.store(enabled ? 1 : 0);
     return LUTGEMM_OK;
 }
 

@@ -27,9 +27,10 @@
 //  share one alpha: 8 lookups are summed, then one FMA (WPG = 2); otherwise one FMA per word.
 //
 //  Result.  fp32 throughout; the 4 lanes that share columns are added with shuffles, the two warp
-//  halves are added through shared memory, each CTA writes its slab's partial sums, and the last CTA
-//  of a column tile adds the slabs in slab order and rounds to fp16 once: no atomics on data, no
-//  memset, run-to-run identical results.
+//  halves are added through shared memory.  Across slabs either (default) vector fp32 reductions in
+//  L2 into one zeroed workspace row, or (ordered mode) one partial row per slab added in slab order
+//  by the last CTA of the column tile, which makes results bit-reproducible run to run.  The last
+//  CTA rounds to fp16 once and leaves the workspace zeroed: no memset launch.
 //
 //  Launch.  The kernel is launched with programmatic stream serialization: its weight stream starts
 //  while the previous kernel in the stream drains; everything a predecessor may have produced (the
@@ -75,7 +76,7 @@ struct Gemv2Params {
     const __half* alpha;     // [G][q][N]
     const __half* q_bias;    // [G][N] or nullptr
     const __half* x;         // [K]
-    float* partial;          // [nslabs][N] split-k workspace
+    float* partial;          // split-k workspace: [nslabs][N] (ordered) or one zeroed row [N] (reductions)
     unsigned* counters;      // [gridDim.x], zero between launches
     int* status;             // device word; set non-zero if a bounded wait ran out
     __half* y16;             // [N] or nullptr
@@ -84,6 +85,7 @@ struct Gemv2Params {
     int n_tile;              // columns per CTA, multiple of kStageCols
     int nslabs;              // gridDim.y
     int a_rows;              // alpha groups per slab (rows of the alpha box): max(1, 512 / g)
+    int ordered;             // 1: slabs are added in slab order (bit-reproducible); 0: fp32 reductions in L2
 };
 
 __device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
@@ -110,6 +112,10 @@ __device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
         "mov.b64 {%0, %1}, rd;\n}\n"
         : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
     return d;
+}
+// Vector fp32 reduction into global memory (performed in L2, no return value).
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 // Programmatic dependent launch: let the next kernel in the stream start launching / wait for the
 // previous one to finish and flush.
@@ -344,14 +350,16 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             asm volatile("bar.sync %0, 64;" ::"r"(2 + cb) : "memory");
             if (h == 0 && rr == 0 && col_ok) {
                 const float4 o = *xchg;
-                *reinterpret_cast<float4*>(part_out + col) =
-                    make_float4(acc[0] + o.x, acc[1] + o.y, acc[2] + o.z, acc[3] + o.w);
+                const float4 r4 = make_float4(acc[0] + o.x, acc[1] + o.y, acc[2] + o.z, acc[3] + o.w);
+                if (p.ordered) *reinterpret_cast<float4*>(part_out + col) = r4;
+                else red_add_v4(p.partial + col, r4);
             }
             asm volatile("bar.sync %0, 64;" ::"r"(2 + cb) : "memory");   // exchange slot free for the next column group
         }
     }
 
-    // Split-k finish: the last CTA of this column tile adds the slabs in slab order.
+    // Split-k finish by the last CTA of this column tile: either add the slabs in slab order, or read
+    // the row of L2-reduced sums and zero it again for the next launch; one fp16 rounding either way.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -365,6 +373,11 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = p.partial + c;
         int sl = 0;
+        if (!p.ordered) {
+            s = __ldcg(reinterpret_cast<const float4*>(src));
+            __stcg(reinterpret_cast<float4*>(p.partial + c), make_float4(0.f, 0.f, 0.f, 0.f));
+            sl = p.nslabs;
+        }
         for (; sl + 8 <= p.nslabs; sl += 8) {
             float4 v[8];
 #pragma unroll
