@@ -1,0 +1,54 @@
+// Written the way the reference's benchmark uses the library (tests/opt/fp16/int3_col_wise_matmul_fp16.cu:
+// parsing at :70, matmul at :123, managed buffers at :246-256), compiled against include/lutGEMM.
+// Prints "shim ok <max abs diff>" and returns 0 when the GPU result matches a host fp32 evaluation.
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "lutGEMM"
+
+int main() {
+    const int M = 1, N = 512, K = 1024, NB = 3, GS = 128, G = K / GS;
+    std::vector<uint32_t> bW((size_t)K / 32 * NB * N);
+    std::vector<float> alpha((size_t)G * NB * N), q_bias((size_t)G * N), x(K);
+    uint32_t s = 12345u;
+    auto rnd = [&]() { s = s * 1664525u + 1013904223u; return s; };
+    for (auto& w : bW) w = rnd();
+    for (auto& a : alpha) a = __half2float(__float2half((rnd() >> 8) * (0.04f / 16777216.0f)));
+    for (auto& b : q_bias) b = __half2float(__float2half(((int)(rnd() >> 8) - 8388608) * (0.02f / 8388608.0f)));
+    for (auto& v : x) v = __half2float(__float2half(((int)(rnd() >> 8) - 8388608) * (1.0f / 8388608.0f)));
+
+    __half *d_in, *d_out;
+    if (cudaMallocManaged(&d_in, sizeof(__half) * M * K) != cudaSuccess) { printf("no device\n"); return 2; }
+    cudaMallocManaged(&d_out, sizeof(__half) * M * N);
+    for (int k = 0; k < K; k++) d_in[k] = __float2half(x[k]);
+
+    lutGEMM::nQWeight_fp16 nqW;
+    nqW.parsing(bW.data(), alpha.data(), K, N, NB, false, G, q_bias.data());
+    if (lutGEMM::last_status() != 0) { printf("parsing failed: %s\n", lutgemm_status_string(lutGEMM::last_status())); return 1; }
+    lutGEMM::matmul((void*)d_out, (void*)d_in, nqW, M);
+    cudaDeviceSynchronize();
+    if (lutGEMM::last_status() != 0) { printf("matmul failed: %s\n", lutgemm_status_string(lutGEMM::last_status())); return 1; }
+
+    double max_diff = 0;
+    for (int n = 0; n < N; n++) {
+        float acc = 0;
+        for (int k = 0; k < K; k++) {
+            float w = q_bias[(size_t)(k / GS) * N + n];
+            for (int b = 0; b < NB; b++) {
+                float sgn = ((bW[((size_t)(k / 32) * NB + b) * N + n] >> (k % 32)) & 1) ? 1.f : -1.f;
+                w += alpha[((size_t)(k / GS) * NB + b) * N + n] * sgn;
+            }
+            acc += x[k] * w;
+        }
+        max_diff = std::fmax(max_diff, std::fabs(acc - __half2float(d_out[n])));
+    }
+    std::vector<__half> dense((size_t)K * N);
+    lutGEMM::dequantize_cpu(nqW, dense.data());
+    printf("shim ok %.3e fields %d %d %d %d %d\n", max_diff, nqW.mSize, nqW.kSize, nqW.nb, nqW.num_groups, nqW.group_size);
+    cudaFree(d_in); cudaFree(d_out);
+    return (max_diff < 5e-3 && lutGEMM::last_status() == 0) ? 0 : 1;
+}
