@@ -98,6 +98,33 @@ int lutgemm_matmul_f32(float* out_f32, const void* in_fp16, lutgemm_weight_t w, 
  * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256). */
 int lutgemm_matmul_host(void* out_fp16_host, const void* in_fp16_host, lutgemm_weight_t w, int m);
 
+/* Matvec (m = 1) that allocates nothing: out[N] (fp16) = in[K] (fp16) x W, with every array passed
+ * by the caller as a device pointer in the container's layout (d_bW uint32 [K/32][q][N], d_alpha fp16
+ * [G][q][N], d_q_bias fp16 [G][N] or NULL).  It has no counterpart in the reference, whose matvec needs
+ * a parsed container and a memset before each call.
+ *
+ * It is meant for programs that must not call cudaMalloc once they are running: a serving process that
+ * has handed all free device memory to its own pool at start-up (a later cudaMalloc would fail, or
+ * would stall every stream while the driver maps new memory), or a host whose rules freeze the memory
+ * map after initialisation.  The other matvec entry points keep a split-k workspace that
+ * lutgemm_weight_create allocates; here that workspace is a fixed array inside the library image
+ * (about 272 KB, resident on every GPU that loads the library until the process exits).  The call
+ * makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *   - N <= 65536 (LUTGEMM_ERR_TOO_LARGE beyond: the array holds one fp32 row of that width); N % 8 == 0
+ *     and a group size that divides 512 or is a multiple of 512 (LUTGEMM_ERR_SHAPE otherwise);
+ *     16-byte aligned pointers (LUTGEMM_ERR_ALIGN).
+ *   - The first call on each device looks up the array's device address (that device must be current);
+ *     make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  Each call clears the part it uses on `stream` before
+ *     the kernel, so a call never sees the previous call's sums, but two calls that can run at the same
+ *     time on the GPU (different streams, no ordering between them) corrupt each other: order them.
+ *   - k-slabs are added by fp32 reductions in L2 (unordered), as in the default mode of lutgemm_matmul. */
+int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uint32_t* d_bW,
+                                  const void* d_alpha_fp16, const void* d_q_bias_fp16,
+                                  int K, int N, int num_bits, int num_alpha_groups, void* stream);
+
 /* Dense fp16 weight on the device: W[k][N] (column-wise) or W[n][K] (row-wise),
  * W = sum_b +-alpha, fp32 sum over planes b = 0..q-1 and one fp16 rounding, no q_bias.
  * Replaces lutGEMM::dequantize_gpu (lutGEMM/src/nQWeight_fp16.cu:29-35) and is bit-identical to

@@ -15,7 +15,7 @@ ERR_NULL, ERR_SHAPE, ERR_BITS, ERR_BATCH, ERR_CUDA, ERR_NO_DEVICE, ERR_TOO_LARGE
 # every symbol include/lutgemm_b200.h declares
 SYMBOLS = (
     "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
-    "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_dequantize",
+    "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matvec_static_scratch", "lutgemm_dequantize",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
@@ -61,6 +61,7 @@ def lib():
     L.lutgemm_matmul.argtypes = [vp, vp, vp, ip, vp]
     L.lutgemm_matmul_f32.argtypes = [vp, vp, vp, ip, vp]
     L.lutgemm_matmul_host.argtypes = [vp, vp, vp, ip]
+    L.lutgemm_matvec_static_scratch.argtypes = [vp, vp, vp, vp, vp, ip, ip, ip, ip, vp]
     L.lutgemm_dequantize.argtypes = [vp, vp, vp]
     L.lutgemm_pack_planes.argtypes = [vp, ip, ip, ip, vp]
     L.lutgemm_pack_planes_device.argtypes = [vp, ip, ip, ip, vp, vp]

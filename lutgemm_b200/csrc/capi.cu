@@ -252,6 +252,32 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
     return LUTGEMM_ERR_BITS;
 }
 
+// ---- scratch for lutgemm_matvec_static_scratch: lives in the library image, never allocated ----
+constexpr int kStaticMaxN = 65536;                       // widest output the static entry point takes
+constexpr size_t kStaticRowBytes = (size_t)kStaticMaxN * sizeof(float);
+constexpr size_t kStaticCounterBytes = (size_t)kMaxCounters * sizeof(unsigned);
+constexpr size_t kStaticScratchBytes = kStaticRowBytes + kStaticCounterBytes + 256;
+// [0, 256 KB): the split-k reduction row; then the per-tile arrival counters; then the status word.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use, so the address is asked for once per
+// device (with that device current) and cached.
+int static_scratch_address(unsigned char** out) {
+    static unsigned char* cached[64] = {};
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return LUTGEMM_ERR_TOO_LARGE;
+    if (!cached[dev]) {
+        unsigned char* ptr = nullptr;
+        LG_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+        if (!ptr) return LUTGEMM_ERR_CUDA;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return LUTGEMM_OK;
+}
+
 int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int m, void* stream) {
     if (!w || !in || (!y16 && !y32)) return LUTGEMM_ERR_NULL;
     if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
@@ -403,6 +429,52 @@ int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w,
     LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, 0));
     LG_CUDA(cudaStreamSynchronize(0));
     return LUTGEMM_OK;
+}
+
+int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uint32_t* d_bW, const void* d_alpha_fp16,
+                                  const void* d_q_bias_fp16, int K, int N, int num_bits, int num_alpha_groups,
+                                  void* stream) {
+    if (!out_fp16 || !in_fp16 || !d_bW || !d_alpha_fp16) return LUTGEMM_ERR_NULL;
+    int n_chk = 0, k_chk = 0;
+    int rc = check_shape(K, N, num_bits, 0, num_alpha_groups, &n_chk, &k_chk);
+    if (rc != LUTGEMM_OK) return rc;
+    if (N > kStaticMaxN) return LUTGEMM_ERR_TOO_LARGE;          // the reduction row holds kStaticMaxN floats
+    if (((uintptr_t)out_fp16 & 15) || ((uintptr_t)in_fp16 & 15) || ((uintptr_t)d_bW & 15) ||
+        ((uintptr_t)d_alpha_fp16 & 15) || ((uintptr_t)d_q_bias_fp16 & 15))
+        return LUTGEMM_ERR_ALIGN;
+    // A container that lives on this stack frame only: it borrows the caller's arrays and the static scratch.
+    lutgemm_weight w;
+    w.bW = const_cast<uint32_t*>(d_bW);
+    w.alpha = (__half*)const_cast<void*>(d_alpha_fp16);
+    w.q_bias = (__half*)const_cast<void*>(d_q_bias_fp16);
+    w.N = N; w.K = K; w.q = num_bits; w.G = num_alpha_groups; w.g = K / num_alpha_groups;
+    w.owns = false;
+    make_tensor_maps(&w);
+    if (!w.tma_ok) return LUTGEMM_ERR_SHAPE;                    // needs N % 8 == 0 and a group size the TMA kernel takes
+    unsigned char* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc != LUTGEMM_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // The array keeps whatever the last call left in it: start from zero sums, counters and status.
+    const int nslabs = (K + lg::kSlab2 - 1) / lg::kSlab2;
+    const int n_tile = choose_ntile(N, nslabs, 1, lg::kStageCols);
+    const int tiles = (N + n_tile - 1) / n_tile;
+    LG_CUDA(cudaMemsetAsync(scratch, 0, (size_t)N * sizeof(float), st));
+    LG_CUDA(cudaMemsetAsync(scratch + kStaticRowBytes, 0, (size_t)tiles * sizeof(unsigned), st));
+    LG_CUDA(cudaMemsetAsync(scratch + kStaticRowBytes + kStaticCounterBytes, 0, sizeof(int), st));
+    lg::Gemv2Params p;
+    p.bW = w.bW; p.alpha = w.alpha; p.q_bias = w.q_bias; p.x = (const __half*)in_fp16;
+    p.partial = (float*)scratch;
+    p.counters = (unsigned*)(scratch + kStaticRowBytes);
+    p.status = (int*)(scratch + kStaticRowBytes + kStaticCounterBytes);
+    p.y16 = (__half*)out_fp16; p.y32 = nullptr;
+    p.N = N; p.K = K; p.q = num_bits; p.g = w.g;
+    p.n_tile = n_tile; p.nslabs = nslabs; p.a_rows = w.a_rows;
+    p.ordered = 0;                                              // one reduction row is all the scratch holds
+    dim3 grid(tiles, nslabs);
+    const bool bias = d_q_bias_fp16 != nullptr;
+    if (w.g % 128 == 0) return launch_gemv_tma<2>(&w, p, grid, bias, st);
+    return launch_gemv_tma<1>(&w, p, grid, bias, st);
 }
 
 int lutgemm_dequantize(lutgemm_weight_t w, void* d_fW, void* stream) {
