@@ -51,6 +51,7 @@ def parse():
     ap.add_argument("--q", type=int, default=3)
     ap.add_argument("--g", type=int, default=128)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--m", type=int, default=1, help="activation rows per matmul (1 = the headline matvec)")
     ap.add_argument("--rot", type=int, default=8, help="distinct weight sets cycled per step")
     ap.add_argument("--ntile", type=int, default=0, help="columns per CTA of the matvec (0 = automatic)")
     ap.add_argument("--variant", type=int, default=0, help="0 = bulk-copy fed matvec kernel, 1 = register-streaming kernel")
@@ -63,7 +64,7 @@ def parse():
 
 
 def workload_name(a):
-    return f"bcq_gemv m=1 n={a.n} k={a.k} q={a.q} g={a.g}" + (" +q_bias" if a.bias else "")
+    return f"bcq_gemv m={a.m} n={a.n} k={a.k} q={a.q} g={a.g}" + (" +q_bias" if a.bias else "")
 
 
 def measured_peak():
@@ -205,22 +206,22 @@ def run_ours(a):
     lib.lutgemm_set_gemv_variant(a.variant)
     lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
     lib.lutgemm_set_ordered_reduction(1 if a.ordered else 0)
-    kernel_name = "gemv_tma_kernel" if a.variant == 0 else "gemv_lut_kernel"
+    kernel_name = ("gemv_tma_kernel" if a.variant == 0 else "gemv_lut_kernel") if a.m == 1 else "gemm_tc_kernel"
 
-    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)
+    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, a.m, a.bias)
     rot = max(1, a.rot)
     weights = []
     for i in range(rot):
         bW, alpha, qb = synth.bcq_layer(a.n, a.k, a.q, a.g, seed=synth.seed_for("bench", a.n, a.k, a.q, i + 1000 * rank),
                                         with_bias=a.bias)
         weights.append(L.nQWeight_fp16(bW, alpha, a.k, a.n, a.q, False, a.k // a.g, qb))
-    x_host = synth.activations(1, a.k, seed=123)
+    x_host = synth.activations(a.m, a.k, seed=123)
     x = torch.from_numpy(x_host.view(np.int16)).cuda().view(torch.float16)
-    ys = [torch.empty((1, a.n), dtype=torch.float16, device="cuda") for _ in range(rot)]
+    ys = [torch.empty((a.m, a.n), dtype=torch.float16, device="cuda") for _ in range(rot)]
 
     def step():
         for w, y in zip(weights, ys):
-            L.matmul(y, x, w, 1)
+            L.matmul(y, x, w, a.m)
 
     def barrier():
         if dist is not None:
@@ -273,10 +274,10 @@ def run_ours(a):
     e2e = None
     if not a.no_e2e:
         xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
-        yout = torch.empty((1, a.n), dtype=torch.int16).pin_memory()
+        yout = torch.empty((a.m, a.n), dtype=torch.int16).pin_memory()
         def e2e_step():
             for w in weights:
-                capi.check(lib.lutgemm_matmul_host(yout.data_ptr(), xin.data_ptr(), w.handle, 1), "matmul_host")
+                capi.check(lib.lutgemm_matmul_host(yout.data_ptr(), xin.data_ptr(), w.handle, a.m), "matmul_host")
         for _ in range(3):
             e2e_step()
         barrier()
@@ -289,8 +290,8 @@ def run_ours(a):
             t = torch.tensor([dt], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
-        e2e = {"value": world * a.steps * rot * B / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": rot * 2 * a.k,
-               "d2h_bytes_per_step": rot * 2 * a.n, "us_per_matvec": dt / (a.steps * rot) * 1e6}
+        e2e = {"value": world * a.steps * rot * B / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": rot * 2 * a.k * a.m,
+               "d2h_bytes_per_step": rot * 2 * a.n * a.m, "us_per_matvec": dt / (a.steps * rot) * 1e6}
         # the result that came back is the device result (up to one fp16 step: the split-k reductions are unordered)
         got = yout.numpy().view(np.float16).astype(np.float32)
         want = ys[-1].float().cpu().numpy()
@@ -322,7 +323,10 @@ def run_ours(a):
     }
     if e2e:
         line["e2e"] = e2e
-    if world == 1 and not a.no_cpu_baseline:
+    if a.m > 1:
+        line["tensor_flops_per_matmul"] = 2.0 * a.m * a.n * a.k * (a.q + (1 if a.bias else 0))
+        line["tensor_TFLOPs"] = line["tensor_flops_per_matmul"] / (us_per_gemv * 1e-6) / 1e12
+    if world == 1 and not a.no_cpu_baseline and a.m == 1:
         threads = 1
         dt, kind, y_cpu = cpu_reference_gemv(a, threads)
         # same seeds as weight set 0 of rank 0: the CPU result doubles as a live parity check

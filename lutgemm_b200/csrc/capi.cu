@@ -16,6 +16,7 @@
 #include "aux_kernels.cuh"
 #include "gemv_lut.cuh"
 #include "gemv_tma.cuh"
+#include "gemm_tc.cuh"
 
 struct lutgemm_weight {
     uint32_t* bW = nullptr;
@@ -33,6 +34,9 @@ struct lutgemm_weight {
     CUtensorMap tmW, tmA;
     bool tma_ok = false;
     int a_rows = 1;            // alpha groups per 512-k slab
+    // fp32 split-k workspace of the batched (tensor-core) path, [tc_rows][N], grown on demand, kept zeroed
+    float* tc_partial = nullptr;
+    int tc_rows = 0;
     // staging for lutgemm_matmul_host
     void* h_stage_in = nullptr;
     void* d_stage_in = nullptr;
@@ -47,6 +51,7 @@ std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_ntile_override{0};
 std::atomic<int> g_pdl{1};
 std::atomic<int> g_ordered{0};
+std::atomic<int> g_batched{1};   // 1: m >= 2 goes to the tensor-core kernel; 0: one matvec per row
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
@@ -252,6 +257,84 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
     return LUTGEMM_ERR_BITS;
 }
 
+template <int Q>
+int launch_gemm_tc_q(const CUtensorMap& tmX, const lg::TcParams& p, dim3 grid, cudaStream_t st) {
+    static bool configured[64] = {};   // the attribute is per device
+    auto kern = lg::gemm_tc_kernel<Q>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemBytes));
+        if (dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, lg::kTcThreads, lg::kTcSmemBytes, st>>>(tmX, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+// Batched rows [0, m), m in 2..128, through the tensor-core kernel.
+int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return LUTGEMM_ERR_CUDA;
+    lg::TcParams p;
+    p.m = m;
+    p.m_pad = (m + 15) / 16 * 16;
+    p.tmem_cols = 32;
+    while (p.tmem_cols < p.m_pad) p.tmem_cols *= 2;
+    CUtensorMap tmX;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)w->K, (cuuint64_t)m};
+        cuuint64_t strides[1] = {(cuuint64_t)w->K * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)p.m_pad};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return LUTGEMM_ERR_CUDA;
+    }
+    const int tiles = (w->N + lg::kTcTileN - 1) / lg::kTcTileN;
+    const int kt_total = (w->K + lg::kTcTileK - 1) / lg::kTcTileK;
+    // split-k factor: fill whole waves of one CTA per SM; among equally full choices take the smallest
+    const int sms = sm_count();
+    int splitk = 1;
+    double best = 0.0;
+    for (int c = 1; c <= 8 && c <= kt_total; c++) {
+        const int ctas = tiles * c;
+        const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
+        if (eff > best + 0.02) { best = eff; splitk = c; }
+    }
+    p.ktiles_per_cta = (kt_total + splitk - 1) / splitk;
+    splitk = (kt_total + p.ktiles_per_cta - 1) / p.ktiles_per_cta;
+    if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
+    if (splitk > 1 && w->tc_rows < m) {
+        // grow the zeroed fp32 workspace (synchronises; happens once per container and batch size class)
+        if (w->tc_partial) LG_CUDA(cudaFree(w->tc_partial));
+        w->tc_partial = nullptr;
+        w->tc_rows = 0;
+        const int rows = (m + 15) / 16 * 16;
+        LG_CUDA(cudaMalloc(&w->tc_partial, (size_t)rows * w->N * sizeof(float)));
+        LG_CUDA(cudaMemset(w->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
+        w->tc_rows = rows;
+    }
+    p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias;
+    p.partial = w->tc_partial; p.counters = w->counters; p.status = w->status;
+    p.y16 = y16; p.y32 = y32;
+    p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
+    dim3 grid(tiles, splitk);
+    switch (w->q) {
+        case 1: return launch_gemm_tc_q<1>(tmX, p, grid, st);
+        case 2: return launch_gemm_tc_q<2>(tmX, p, grid, st);
+        case 3: return launch_gemm_tc_q<3>(tmX, p, grid, st);
+        case 4: return launch_gemm_tc_q<4>(tmX, p, grid, st);
+        case 5: return launch_gemm_tc_q<5>(tmX, p, grid, st);
+        case 6: return launch_gemm_tc_q<6>(tmX, p, grid, st);
+        case 7: return launch_gemm_tc_q<7>(tmX, p, grid, st);
+        case 8: return launch_gemm_tc_q<8>(tmX, p, grid, st);
+    }
+    return LUTGEMM_ERR_BITS;
+}
+
 // ---- scratch for lutgemm_matvec_static_scratch: lives in the library image, never allocated ----
 constexpr int kStaticMaxN = 65536;                       // widest output the static entry point takes
 constexpr size_t kStaticRowBytes = (size_t)kStaticMaxN * sizeof(float);
@@ -284,9 +367,19 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     if (((uintptr_t)in & 15) || ((uintptr_t)y16 & 15) || ((uintptr_t)y32 & 15)) return LUTGEMM_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     const __half* x = (const __half*)in;
-    for (int r = 0; r < m; r++) {
-        int rc = gemv_row(w, x + (size_t)r * w->K, y16 ? y16 + (size_t)r * w->N : nullptr,
-                          y32 ? y32 + (size_t)r * w->N : nullptr, st);
+    if (m == 1 || g_batched.load() == 0) {
+        for (int r = 0; r < m; r++) {
+            int rc = gemv_row(w, x + (size_t)r * w->K, y16 ? y16 + (size_t)r * w->N : nullptr,
+                              y32 ? y32 + (size_t)r * w->N : nullptr, st);
+            if (rc != LUTGEMM_OK) return rc;
+        }
+        return LUTGEMM_OK;
+    }
+    // batched: 128 rows per tensor-core launch
+    for (int r0 = 0; r0 < m; r0 += 128) {
+        const int rows = (m - r0 < 128) ? (m - r0) : 128;
+        int rc = gemm_tc_rows(w, x + (size_t)r0 * w->K, y16 ? y16 + (size_t)r0 * w->N : nullptr,
+                              y32 ? y32 + (size_t)r0 * w->N : nullptr, rows, st);
         if (rc != LUTGEMM_OK) return rc;
     }
     return LUTGEMM_OK;
@@ -386,6 +479,7 @@ int lutgemm_weight_destroy(lutgemm_weight_t w) {
     if (w->partial) cudaFree(w->partial);
     if (w->counters) cudaFree(w->counters);
     if (w->status) cudaFree(w->status);
+    if (w->tc_partial) cudaFree(w->tc_partial);
     if (w->h_stage_in) cudaFreeHost(w->h_stage_in);
     if (w->d_stage_in) cudaFree(w->d_stage_in);
     if (w->d_stage_out) cudaFree(w->d_stage_out);
@@ -641,6 +735,11 @@ int lutgemm_set_gemv_variant(int variant) {
 
 int lutgemm_set_ordered_reduction(int enabled) {
     g_ordered.store(enabled ? 1 : 0);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_set_batched_path(int enabled) {
+    g_batched.store(enabled ? 1 : 0);
     return LUTGEMM_OK;
 }
 
