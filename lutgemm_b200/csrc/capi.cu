@@ -259,13 +259,14 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
 
 template <int Q>
 int launch_gemm_tc_q(const CUtensorMap& tmX, const lg::TcParams& p, dim3 grid, cudaStream_t st) {
-    static bool configured[64] = {};   // the attribute is per device
-    auto kern = lg::gemm_tc_kernel<Q>;
+    static bool configured[64][2] = {};   // the attribute is per device
+    const bool bias = p.q_bias != nullptr;
+    auto kern = bias ? lg::gemm_tc_kernel<Q, true> : lg::gemm_tc_kernel<Q, false>;
     int dev = 0;
     LG_CUDA(cudaGetDevice(&dev));
-    if (dev >= 64 || !configured[dev]) {
+    if (dev >= 64 || !configured[dev][bias]) {
         LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemBytes));
-        if (dev < 64) configured[dev] = true;
+        if (dev < 64) configured[dev][bias] = true;
     }
     kern<<<grid, lg::kTcThreads, lg::kTcSmemBytes, st>>>(tmX, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -34,12 +34,12 @@ namespace lg {
 constexpr int kTcTileN = 128;                 // output columns per CTA (MMA M)
 constexpr int kTcTileK = 128;                 // k per stage: two 64-k swizzle atoms
 constexpr int kTcStages = 3;
-constexpr int kTcPrefetch = 8;                // stages of packed words / scales in flight per thread
 constexpr int kTcExpWarps = 16;
 constexpr int kTcThreads = (kTcExpWarps + 2) * 32;       // + TMA warp + MMA warp = 576
 constexpr int kTcAStageBytes = kTcTileN * kTcTileK * 2;   // 32768: [2 halves][128 rows][128 B]
-constexpr int kTcBHalfBytesMax = 128 * 128;              // m_pad rows x 128 B, m_pad <= 128
-constexpr int kTcBarOff = kTcStages * kTcAStageBytes + kTcStages * 2 * kTcBHalfBytesMax;   // 98304 + 98304
+constexpr int kTcBRingBytes = 98304;                     // activation ring: one slot per k tile, [2 halves][m_pad rows][128 B]
+constexpr int kTcBSlotsMax = 8;
+constexpr int kTcBarOff = kTcStages * kTcAStageBytes + kTcBRingBytes;   // 98304 + 98304
 constexpr int kTcSmemBytes = kTcBarOff + 256;
 
 enum { kStatusTcTimeout = 3 };
@@ -112,8 +112,8 @@ __device__ __forceinline__ uint32_t umma_idesc_f16_f32(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-// Q: number of bit planes.  tmX: 2-D map {K, m} of fp16, box {64, m_pad}, 128-byte swizzle.
-template <int Q>
+// Q: number of bit planes; BIAS: container has q_bias.  tmX: 2-D map {K, m} of fp16, box {64, m_pad}, 128-byte swizzle.
+template <int Q, bool BIAS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -121,11 +121,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     const uint32_t a_base = smem_base;
     const uint32_t b_base = smem_base + kTcStages * kTcAStageBytes;
     const uint32_t bar_afull = smem_base + kTcBarOff;            // kTcStages x 8 B, count = expansion warps
-    const uint32_t bar_bfull = bar_afull + 8 * kTcStages;        // TMA transaction barriers
-    const uint32_t bar_empty = bar_bfull + 8 * kTcStages;        // tcgen05.commit arrives
+    const uint32_t bar_empty = bar_afull + 8 * kTcStages;        // weight stage free: tcgen05.commit arrives
     const uint32_t bar_acc = bar_empty + 8 * kTcStages;          // accumulator complete
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcBarOff + 128);
-    int* s_flag = reinterpret_cast<int*>(smem + kTcBarOff + 136);
+    const uint32_t bar_bfull = bar_acc + 8;                      // activation slot loaded (TMA transaction barriers)
+    const uint32_t bar_bempty = bar_bfull + 8 * kTcBSlotsMax;    // activation slot free: tcgen05.commit arrives
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcBarOff + 200);
+    int* s_flag = reinterpret_cast<int*>(smem + kTcBarOff + 208);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int N = p.N;
@@ -135,16 +136,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     const int kt_total = (p.K + kTcTileK - 1) / kTcTileK;
     const int kt_end = min(kt_total, kt_begin + p.ktiles_per_cta);
     const int nkt = kt_end - kt_begin;
-    const int planes = Q + (p.q_bias ? 1 : 0);            // q_bias rides as one more plane
+    constexpr int planes = Q + (BIAS ? 1 : 0);            // q_bias rides as one more plane
     const int nst = nkt * planes;                         // pipeline stages: (k tile, plane) pairs
     const size_t rowN = (size_t)N;
     const uint32_t b_half_bytes = (uint32_t)p.m_pad * 128u;
+    const uint32_t b_slot_bytes = 2u * b_half_bytes;
+    int nb_slots = kTcBRingBytes / (int)b_slot_bytes;          // 3 (m_pad = 128) .. 8
+    if (nb_slots > kTcBSlotsMax) nb_slots = kTcBSlotsMax;
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; s++) {
             mbar_init(bar_afull + 8 * s, kTcExpWarps);
-            mbar_init(bar_bfull + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < kTcBSlotsMax; s++) {
+            mbar_init(bar_bfull + 8 * s, 1);
+            mbar_init(bar_bempty + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
         mbar_fence_init();
@@ -168,102 +175,129 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
         // swizzled position of this thread's four 16-byte chunks: half = ks >> 1, chunks 4 (ks & 1) .. +3
         const uint32_t row_off = (uint32_t)(ks >> 1) * (kTcTileN * 128) + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
         const int c0 = 4 * (ks & 1);
-        // Packed words and scales are fetched kTcPrefetch stages ahead (a stage is far shorter than a trip
-        // to HBM); the queue lives in registers and is indexed at compile time by unrolling the stage loop.
-        uint32_t wq[kTcPrefetch], aq[kTcPrefetch];         // word of the plane; alpha_b (or q_bias) as half2 (a, a)
-        auto load_stage = [&](int i, uint32_t& w, uint32_t& v2) {
-            w = 0u;
-            unsigned short vh = 0;
-            if (i < nst) {
-                const int kt = kt_begin + i / planes, b = i % planes;
-                const int kw = kt * (kTcTileK / 32) + ks;
-                if (n_ok && (kw * 32 < p.K)) {
-                    const int grp = (kw * 32) / p.g;
-                    if (b < Q) {
-                        w = __ldg(p.bW + ((size_t)kw * q + b) * rowN + n);
-                        vh = __ldg(reinterpret_cast<const unsigned short*>(p.alpha) + ((size_t)grp * q + b) * rowN + n);
-                    } else {
-                        vh = __ldg(reinterpret_cast<const unsigned short*>(p.q_bias) + (size_t)grp * rowN + n);
-                    }
-                }
+        // One k tile = `planes` pipeline stages.  The packed words and scales of a k tile are fetched two
+        // tiles ahead into registers (a tile is far shorter than a trip to HBM); plane indices are
+        // compile-time, addresses advance by constant strides.
+        constexpr int P = Q + (BIAS ? 1 : 0);
+        const int g_words = p.g >> 5;                      // group size in packed words
+        int pf_t = 0;                                      // next k tile (local index) to fetch
+        int pf_kw = kt_begin * (kTcTileK / 32) + ks;
+        int pf_grp = pf_kw / g_words, pf_rem = pf_kw - pf_grp * g_words;
+        const uint32_t* wp = p.bW + (size_t)pf_kw * Q * rowN + n;
+        const size_t w_tile_stride = (size_t)(kTcTileK / 32) * Q * rowN;
+        const unsigned short* alpha_u16 = reinterpret_cast<const unsigned short*>(p.alpha) + n;
+        const unsigned short* qbias_u16 = reinterpret_cast<const unsigned short*>(p.q_bias) + n;
+        auto load_tile = [&](uint32_t (&w)[P], uint32_t (&a)[P]) {
+            const bool ok = (pf_t < nkt) && n_ok && (pf_kw * 32 < p.K);
+            const unsigned short* ap = alpha_u16 + (size_t)pf_grp * Q * rowN;
+#pragma unroll
+            for (int b = 0; b < Q; b++) {
+                w[b] = ok ? __ldg(wp + (size_t)b * rowN) : 0u;
+                a[b] = (ok ? (uint32_t)__ldg(ap + (size_t)b * rowN) : 0u) * 0x00010001u;
             }
-            v2 = (uint32_t)vh * 0x00010001u;
+            if (BIAS) {
+                w[Q] = 0u;
+                a[Q] = (ok ? (uint32_t)__ldg(qbias_u16 + (size_t)pf_grp * rowN) : 0u) * 0x00010001u;
+            }
+            pf_t++;
+            pf_kw += kTcTileK / 32;
+            wp += w_tile_stride;
+            pf_rem += kTcTileK / 32;
+            while (pf_rem >= g_words) { pf_rem -= g_words; pf_grp++; }
         };
+        uint32_t chunk_off[4];
 #pragma unroll
-        for (int d = 0; d < kTcPrefetch; d++) load_stage(d, wq[d], aq[d]);
-        for (int i0 = 0; i0 < nst && !timed_out; i0 += kTcPrefetch) {
+        for (int c = 0; c < 4; c++) chunk_off[c] = (uint32_t)(((c0 + c) ^ (row & 7)) * 16);
+        int cs = 0, cround = 0;                            // shared-memory stage and ring round of the next stage
+        auto expand_tile = [&](const uint32_t (&w)[P], const uint32_t (&a)[P]) {
 #pragma unroll
-            for (int d = 0; d < kTcPrefetch; d++) {
-                const int i = i0 + d;
-                if (i >= nst || timed_out) break;
-                const int s = i % kTcStages;
-                const bool is_bias = (i % planes) == Q;
-                const uint32_t word = wq[d], a2 = aq[d];
-                load_stage(i + kTcPrefetch, wq[d], aq[d]);
-                if (i >= kTcStages) {
-                    if (!mbar_wait_bounded(bar_empty + 8 * s, ((i / kTcStages) - 1) & 1)) { timed_out = true; break; }
+            for (int b = 0; b < P; b++) {
+                if (timed_out) break;
+                if (cround > 0) {
+                    if (!mbar_wait_bounded(bar_empty + 8 * cs, (cround - 1) & 1)) { timed_out = true; break; }
                 }
-                // 16 registers of two weights each: element t (low half) and t + 16 (high half) of the word;
-                // bit set -> +alpha, bit clear -> -alpha (sign bits flipped where the bit is 0); q_bias: no sign
-                const uint32_t flip_mask = is_bias ? 0u : 0x80008000u;
-                uint32_t h[16];
-#pragma unroll
-                for (int t = 0; t < 16; t++) {
-                    const uint32_t sh = (t == 15) ? word : (word << (15 - t));
-                    h[t] = a2 ^ (~sh & flip_mask);
-                }
-                // natural k order: (0,1), (2,3), ... then (16,17), ...
+                // two weights per register: element t (low half) and t + 16 (high half) of the word;
+                // bit set -> +alpha, bit clear -> -alpha (sign bit flipped where the bit is 0)
                 uint32_t nat[16];
+                if (b < Q) {
+                    uint32_t h[16];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    nat[j] = prmt_b32(h[2 * j], h[2 * j + 1], 0x5410u);
-                    nat[j + 8] = prmt_b32(h[2 * j], h[2 * j + 1], 0x7632u);
-                }
-                unsigned char* dst = smem + s * kTcAStageBytes + row_off;
+                    for (int t = 0; t < 16; t++) {
+                        const uint32_t sh = (t == 15) ? w[b] : (w[b] << (15 - t));
+                        h[t] = a[b] ^ (~sh & 0x80008000u);
+                    }
+                    // natural k order: (0,1), (2,3), ... then (16,17), ...
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int chunk = (c0 + c) ^ (row & 7);
-                    *reinterpret_cast<uint4*>(dst + chunk * 16) = make_uint4(nat[4 * c], nat[4 * c + 1], nat[4 * c + 2], nat[4 * c + 3]);
+                    for (int j = 0; j < 8; j++) {
+                        nat[j] = prmt_b32(h[2 * j], h[2 * j + 1], 0x5410u);
+                        nat[j + 8] = prmt_b32(h[2 * j], h[2 * j + 1], 0x7632u);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) nat[j] = a[b];   // q_bias plane: the same value, no sign
                 }
+                unsigned char* dst = smem + cs * kTcAStageBytes + row_off;
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4*>(dst + chunk_off[c]) = make_uint4(nat[4 * c], nat[4 * c + 1], nat[4 * c + 2], nat[4 * c + 3]);
                 fence_proxy_async_smem();                  // make the generic-proxy stores visible to the tensor core
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_afull + 8 * s);
+                if (lane == 0) mbar_arrive(bar_afull + 8 * cs);
+                if (++cs == kTcStages) { cs = 0; cround++; }
+            }
+        };
+        uint32_t wA[P], aA[P], wB[P], aB[P];
+        load_tile(wA, aA);
+        load_tile(wB, aB);
+        for (int j = 0; j < nkt && !timed_out; j += 2) {
+            expand_tile(wA, aA);
+            load_tile(wA, aA);
+            if (j + 1 < nkt && !timed_out) {
+                expand_tile(wB, aB);
+                load_tile(wB, aB);
             }
         }
     } else if (warp == kTcExpWarps) {
-        // ---------------- TMA: activation tiles ----------------
+        // ---------------- TMA: activation tiles, one slot per k tile, as far ahead as the ring allows ----------------
         if (lane == 0) {
             tma_prefetch_descriptor(&tmX);
-            for (int i = 0; i < nst; i++) {
-                const int s = i % kTcStages;
-                if (i >= kTcStages) {
-                    if (!mbar_wait_bounded(bar_empty + 8 * s, ((i / kTcStages) - 1) & 1)) { timed_out = true; break; }
+            int slot = 0, round = 0;
+            for (int j = 0; j < nkt; j++) {
+                if (round > 0) {
+                    if (!mbar_wait_bounded(bar_bempty + 8 * slot, (round - 1) & 1)) { timed_out = true; break; }
                 }
-                const int k = (kt_begin + i / planes) * kTcTileK;     // the same activation tile for every plane of a k tile
-                mbar_arrive_expect_tx(bar_bfull + 8 * s, 2 * b_half_bytes);
-                tma_load_2d(b_base + s * 2 * kTcBHalfBytesMax, &tmX, k, 0, bar_bfull + 8 * s);
-                tma_load_2d(b_base + s * 2 * kTcBHalfBytesMax + kTcBHalfBytesMax, &tmX, k + 64, 0, bar_bfull + 8 * s);
+                const int k = (kt_begin + j) * kTcTileK;
+                const uint32_t dst = b_base + slot * b_slot_bytes;
+                mbar_arrive_expect_tx(bar_bfull + 8 * slot, b_slot_bytes);
+                tma_load_2d(dst, &tmX, k, 0, bar_bfull + 8 * slot);
+                tma_load_2d(dst + b_half_bytes, &tmX, k + 64, 0, bar_bfull + 8 * slot);
+                if (++slot == nb_slots) { slot = 0; round++; }
             }
         }
     } else {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16_f32(p.m_pad);
-            for (int i = 0; i < nst; i++) {
-                const int s = i % kTcStages;
-                const uint32_t ph = (i / kTcStages) & 1;
-                if (!mbar_wait_bounded(bar_afull + 8 * s, ph) || !mbar_wait_bounded(bar_bfull + 8 * s, ph)) { timed_out = true; break; }
-                tc_fence_after_sync();
+            int s = 0, sround = 0, bslot = 0, bround = 0;
+            for (int j = 0; j < nkt && !timed_out; j++) {
+                if (!mbar_wait_bounded(bar_bfull + 8 * bslot, bround & 1)) { timed_out = true; break; }
+                for (int b = 0; b < planes; b++) {
+                    if (!mbar_wait_bounded(bar_afull + 8 * s, sround & 1)) { timed_out = true; break; }
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
+                    for (int half = 0; half < 2; half++) {
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; k16++) {
-                        const uint64_t da = umma_desc_k_sw128(a_base + s * kTcAStageBytes + half * (kTcTileN * 128) + k16 * 32);
-                        const uint64_t db = umma_desc_k_sw128(b_base + s * 2 * kTcBHalfBytesMax + half * kTcBHalfBytesMax + k16 * 32);
-                        umma_f16_ss(tmem_acc, da, db, idesc, (i > 0 || half > 0 || k16 > 0) ? 1u : 0u);
+                        for (int k16 = 0; k16 < 4; k16++) {
+                            const uint64_t da = umma_desc_k_sw128(a_base + s * kTcAStageBytes + half * (kTcTileN * 128) + k16 * 32);
+                            const uint64_t db = umma_desc_k_sw128(b_base + bslot * b_slot_bytes + half * b_half_bytes + k16 * 32);
+                            umma_f16_ss(tmem_acc, da, db, idesc, (j > 0 || b > 0 || half > 0 || k16 > 0) ? 1u : 0u);
+                        }
                     }
+                    umma_commit(bar_empty + 8 * s);        // weight stage reusable once these MMAs have read it
+                    if (++s == kTcStages) { s = 0; sround++; }
                 }
-                umma_commit(bar_empty + 8 * s);            // stage reusable once these MMAs have read it
+                umma_commit(bar_bempty + 8 * bslot);       // activation slot reusable after the last plane of the k tile
+                if (++bslot == nb_slots) { bslot = 0; bround++; }
             }
             umma_commit(bar_acc);                          // accumulator complete
         }
