@@ -46,6 +46,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack"],
+                    help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more")
+    ap.add_argument("--layers", type=int, default=96, help="decoder layers of the stack workload")
+    ap.add_argument("--hidden", type=int, default=12288)
+    ap.add_argument("--ffn", type=int, default=49152)
     ap.add_argument("--n", type=int, default=12288)
     ap.add_argument("--k", type=int, default=12288)
     ap.add_argument("--q", type=int, default=3)
@@ -183,6 +188,113 @@ def run_reference(a):
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def run_stack(a):
+    """Tensor-parallel decoder linear stack (BASELINE config 5): `layers` x {QKV, out, FC1, FC2} at m = 1, sharded over
+    the ranks (column-parallel + all-gather, row-parallel + all-reduce).  Strong scaling: the stack is the same at every N.
+    value = algorithmic bytes of the whole stack / step time (max over ranks), i.e. aggregate effective GB/s."""
+    import torch
+    import torch.distributed as dist
+    from lutgemm_b200 import capi, tp_stack
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    lib = capi.lib()
+    lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
+    stack = tp_stack.TPLinearStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    B = tp_stack.stack_algorithmic_bytes(a.hidden, a.ffn, a.q, a.g, a.layers)
+    x_host = synth.activations(1, a.hidden, seed=5).reshape(-1)
+    x = torch.from_numpy(x_host.view(np.int16).copy()).cuda().view(torch.float16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, a.warmup)):
+        stack.step(x)
+    barrier()
+    run_step, graph = (lambda: stack.step(x)), None
+    if not a.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                stack.step(x)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    stack.step(x)
+            torch.cuda.current_stream().wait_stream(side)
+            run_step = graph.replay
+            for _ in range(2):
+                run_step()
+        except Exception as e:          # capture of the collectives refused: time eager launches instead
+            graph, run_step = None, (lambda: stack.step(x))
+            if rank == 0:
+                print(f"bench.py: CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
+        barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(a.steps):
+        run_step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sec_per_step = ms / 1e3 / a.steps
+    # end to end: the step's activation vector comes from pinned host memory and its result goes back every step
+    xin = torch.from_numpy(x_host.view(np.int16).copy()).pin_memory()
+    yout = torch.empty(a.hidden, dtype=torch.int16).pin_memory()
+    xdev = torch.empty(a.hidden, dtype=torch.float16, device="cuda")
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        xdev.view(torch.int16).copy_(xin, non_blocking=True)
+        y = stack.step(xdev)
+        yout.copy_(y.view(torch.int16), non_blocking=True)
+        torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        value = B / sec_per_step / 1e9
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(3, a.warmup),
+            "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"tensor-parallel decoder linear stack, {a.layers} layers, hidden {a.hidden}, ffn {a.ffn}, "
+                                   f"q={a.q} g={a.g} m=1", "parallelism": f"tp{world}: QKV/FC1 column-parallel + all-gather, "
+                                   "out-proj/FC2 row-parallel + all-reduce (NCCL)", "algorithmic_bytes_per_step": B,
+                       "l2": f"{B / world / 1e9:.1f} GB of packed weights per GPU per step, far larger than L2",
+                       "launch": "python" if graph is None else "cuda graph of one step, replayed"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_source": peak_kind, "traffic": None, "kernel": "gemv_tma_kernel (per GPU average over the step, collectives included)"},
+            "gpu_launches": int(a.steps * a.layers * 4),
+            "clocks": clocks,
+            "e2e": {"value": B * a.steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * a.hidden, "d2h_bytes_per_step": 2 * a.hidden},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_ours(a):
@@ -346,4 +458,9 @@ if __name__ == "__main__":
     if args.impl == "reference":
         run_reference(args)
     else:
-        run_ours(args)
+        world_size = int(os.environ.get("WORLD_SIZE", "1"))
+        workload = args.workload if args.workload != "auto" else ("gemv" if world_size == 1 else "stack")
+        if workload == "stack":
+            run_stack(args)
+        else:
+            run_ours(args)

@@ -1,0 +1,116 @@
+"""Tensor-parallel sharding of the BCQ linears: shard algebra on the host, a world_size-2 run over gloo
+on CPU ranks (host stand-ins for the matvec), and the real kernels on one GPU (and on two when present)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from lutgemm_b200 import synth, tp_stack
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_column_and_row_shards_recombine():
+    N, K, q, g, P = 64, 512, 3, 128, 4
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=5, with_bias=True)
+    x = synth.activations(1, K, seed=2)
+    a_h, qb_h = alpha.astype(np.float16), qb.astype(np.float16)
+    full = oracle.bcq_matmul_fp32(x, bW, a_h, qb_h, g)
+    cols = []
+    for r in range(P):
+        sb, sa, sq = tp_stack.shard_columns(bW, alpha, qb, P, r)
+        cols.append(oracle.bcq_matmul_fp32(x, sb, sa.astype(np.float16), sq.astype(np.float16), g))
+    np.testing.assert_allclose(np.concatenate(cols, axis=1), full, rtol=0, atol=0)          # columns are independent
+    rows = []
+    for r in range(P):
+        sb, sa, sq = tp_stack.shard_rows(bW, alpha, qb, g, P, r)
+        xs = np.ascontiguousarray(x[:, r * (K // P):(r + 1) * (K // P)])
+        rows.append(oracle.bcq_matmul_fp32(xs, sb, sa.astype(np.float16), sq.astype(np.float16), g))
+    np.testing.assert_allclose(np.sum(rows, axis=0), full, rtol=1e-5, atol=1e-5)             # the k-sum is associative
+    with pytest.raises(ValueError):
+        tp_stack.shard_rows(bW, alpha, qb, g, 8, 0)       # K/P = 64 is not a whole group
+    with pytest.raises(ValueError):
+        tp_stack.shard_columns(bW, alpha, qb, 16, 0)      # N/P = 4 columns
+
+
+def test_stack_bytes_match_published_figure():
+    assert tp_stack.stack_algorithmic_bytes(12288, 49152, 3, 128, 1) == 764805120
+    assert tp_stack.stack_algorithmic_bytes(12288, 49152, 3, 128, 96) == 73421291520
+
+
+WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["LG_ROOT"])
+from lutgemm_b200 import synth, tp_stack
+from oracle import oracle
+
+def host_container(bW, alpha, n_loc, k_loc):
+    return {"bW": bW, "alpha": alpha.astype(np.float16)}
+def mv(out, x, w):
+    y = oracle.bcq_matmul_fp32(x.numpy().reshape(1, -1), w["bW"], w["alpha"], None, G)
+    out.copy_(torch.from_numpy(y.reshape(-1)).to(out.dtype))
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+H, F, Q, G, LAYERS = 256, 512, 2, 64, 2
+st = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, rank=rank, world=world, device="cpu", seed=3,
+                            matvec=mv, matvec_f32=mv, make_container=host_container, generate="host")
+x = torch.from_numpy(synth.activations(1, H, seed=9).reshape(-1).copy())
+y = st.step(x).clone()
+ref = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, rank=0, world=1, device="cpu", seed=3,
+                             matvec=mv, matvec_f32=mv, make_container=host_container, generate="host")
+y1 = ref.step(x).clone()
+err = float((y.float() - y1.float()).abs().max()); scale = float(y1.float().abs().max())
+gathered = [torch.empty_like(y) for _ in range(world)]
+dist.all_gather(gathered, y)
+same = all(torch.equal(gathered[0], t) for t in gathered)
+print(f"RESULT rank={rank} err={err:.3e} scale={scale:.3e} same={same}", flush=True)
+dist.destroy_process_group()
+'''
+
+
+def test_two_rank_stack_over_gloo_matches_single_rank(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, LG_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29613", WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
+        line = [l for l in o.splitlines() if l.startswith("RESULT")][0]
+        f = dict(kv.split("=") for kv in line.split()[1:])
+        assert f["same"] == "True"                                  # every rank ends with the same activations
+        assert float(f["err"]) <= 2e-3 * float(f["scale"]) + 1e-3   # fp16 roundings of the intermediate vectors only
+
+
+@pytest.mark.gpu
+def test_single_gpu_stack_matches_host_chain():
+    torch = pytest.importorskip("torch")
+    H, F, Q, G, LAYERS = 512, 1024, 3, 128, 2
+    st = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, device="cuda", seed=1, generate="host")
+    x = synth.activations(1, H, seed=4)
+    y = st.step(torch.from_numpy(x.view(np.int16)).cuda().view(torch.float16).reshape(-1)).float().cpu().numpy()
+    # the same chain on the host with the fp32 reference and the same fp16 roundings between linears
+    cur = x
+    for layer in range(LAYERS):
+        outs = {}
+        for idx, (name, N, K, mode) in enumerate(st.shapes):
+            bW, alpha, _ = synth.bcq_layer(N, K, Q, G, seed=synth.seed_for("stack", N, K, Q, 131 * layer + idx + 1),
+                                           alpha_std=1.0 / np.sqrt(K * Q))
+            inp = cur if name in ("qkv", "fc1") else outs["prev"]
+            if name == "out":
+                inp = np.ascontiguousarray(outs["qkv"][:, :H])
+            if name == "fc2":
+                inp = outs["fc1"]
+            yv = oracle.bcq_matmul_fp32(inp, bW, alpha.astype(np.float16), None, G).astype(np.float16)
+            outs[name] = yv
+            outs["prev"] = yv
+            if name == "out":
+                cur = yv
+        cur = outs["fc2"]
+    ref = cur.astype(np.float32).reshape(-1)
+    assert np.abs(y - ref).max() <= 1e-2 * np.abs(ref).max() + 1e-3
