@@ -190,6 +190,28 @@ def run_reference(a):
     print(json.dumps(line), flush=True)
 
 
+def shutdown_process_group(dist_mod):
+    """Leaves the process group without risking a hang at exit: the captured graphs that hold NCCL kernels are
+    gone by now (the caller dropped them); if the communicator tear-down still does not finish, the process
+    exits anyway (the JSON line has already been flushed)."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if dist_mod is None:
+        return
+    done = threading.Event()
+
+    def _destroy():
+        try:
+            dist_mod.destroy_process_group()
+        except Exception:
+            pass
+        done.set()
+
+    threading.Thread(target=_destroy, daemon=True).start()
+    if not done.wait(30.0):
+        os._exit(0)
+
+
 def run_stack(a):
     """Tensor-parallel decoder linear stack (BASELINE config 5): `layers` x {QKV, out, FC1, FC2} at m = 1, sharded over
     the ranks (column-parallel + all-gather, row-parallel + all-reduce).  Strong scaling: the stack is the same at every N.
@@ -293,8 +315,10 @@ def run_stack(a):
             "e2e": {"value": B * a.steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * a.hidden, "d2h_bytes_per_step": 2 * a.hidden},
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    graph = None
+    run_step = None
+    torch.cuda.synchronize()
+    shutdown_process_group(dist if world > 1 else None)
 
 
 def run_ours(a):
@@ -411,8 +435,10 @@ def run_ours(a):
                       + 4e-6 * float(np.sqrt((want ** 2).mean())))
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        graph = None
+        run_step = None
+        torch.cuda.synchronize()
+        shutdown_process_group(dist)
         return
 
     peak, peak_kind = measured_peak()
@@ -449,8 +475,10 @@ def run_ours(a):
                                           "(dequantize_cpu + serial-k fp32 matmul)", "seconds": dt,
                                 "max_abs_diff_vs_gpu_over_rms": float(np.abs(y_cpu - y_gpu).max() / rms)}
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    graph = None
+    run_step = None
+    torch.cuda.synchronize()
+    shutdown_process_group(dist)
 
 
 if __name__ == "__main__":
