@@ -125,6 +125,48 @@ int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uin
                                   const void* d_alpha_fp16, const void* d_q_bias_fp16,
                                   int K, int N, int num_bits, int num_alpha_groups, void* stream);
 
+/* ---- Tensor-parallel matvec: the exchange steps fused into the kernel (no counterpart in the reference,
+ * which is single-GPU; lutGEMM/CMakeLists.txt:13 links no communication library). ----
+ *
+ * A decoder linear sharded over `world` GPUs (one process each) needs an all-gather after a column-parallel
+ * matvec and an all-reduce after a row-parallel one.  Instead of separate collectives, the producing kernel
+ * stores its result straight into every rank's buffer (peer-mapped pointers, see lutgemm_ipc_*) and bumps a
+ * flag there; the consuming kernel starts streaming its weights at once and waits for the flag (bounded)
+ * only before it reads the activations.
+ *   x_mode   0: `in_fp16` is ready in stream order.  1: `in_fp16` (local memory) is filled by all ranks' pushes;
+ *            wait until *flag_in >= flag_target.  2: the input is sum_r x_slots[r*x_slot_stride + x_off + k]
+ *            (fp32 rows pushed by the ranks, added in rank order, rounded to fp16 once); same wait.
+ *   out_mode 0: out_fp16 / out_f32 in local memory.  1: fp16 result to out16[r] + out_off for every rank r.
+ *            2: fp32 result to out32[r] (this rank's row on rank r).  Then *flag_out[r] += 1 per finished column
+ *            tile (lutgemm_matvec_tiles gives the count; the consumer's flag_target is the sum over producers).
+ * The kernel re-arms flag_in (and done_counter, a zeroed word of the caller's) itself, so a CUDA graph with
+ * constant arguments can be replayed.  Needs a container the TMA-fed kernel takes; world <= 8. */
+typedef struct lutgemm_tp_link {
+    int x_mode, out_mode, world, out_off;
+    const float* x_slots;
+    int x_slot_stride, x_off;
+    unsigned* flag_in;
+    unsigned flag_target;
+    unsigned* done_counter;
+    void* out16[8];
+    float* out32[8];
+    unsigned* flag_out[8];
+} lutgemm_tp_link;
+int lutgemm_matvec_tp(const void* in_fp16, lutgemm_weight_t w, const lutgemm_tp_link* link, void* out_fp16,
+                      float* out_f32, void* stream);
+/* Column tiles (= flag increments per launch) of the TMA-fed matvec on this container. */
+int lutgemm_matvec_tiles(lutgemm_weight_t w, int* tiles);
+/* Last consumer of a chain: waits for the flag, adds `world` fp32 rows of n values in rank order, writes fp16
+ * and/or fp32, re-arms the flag.  `status_owner` receives a time-out in its status word. */
+int lutgemm_tp_finalize(void* out_fp16, float* out_f32, const float* slots, int slot_stride, int world, int n,
+                        unsigned* flag_in, unsigned flag_target, lutgemm_weight_t status_owner, void* stream);
+/* Peer-visible device memory: allocate (zero-filled) and export a 64-byte handle / map another process's
+ * handle into this process / unmap / free. */
+int lutgemm_ipc_alloc(size_t bytes, void** dptr, void* handle64);
+int lutgemm_ipc_open(const void* handle64, void** dptr);
+int lutgemm_ipc_close(void* dptr);
+int lutgemm_ipc_free(void* dptr);
+
 /* Dense fp16 weight on the device: W[k][N] (column-wise) or W[n][K] (row-wise),
  * W = sum_b +-alpha, fp32 sum over planes b = 0..q-1 and one fp16 rounding, no q_bias.
  * Replaces lutGEMM::dequantize_gpu (lutGEMM/src/nQWeight_fp16.cu:29-35) and is bit-identical to

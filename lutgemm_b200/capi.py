@@ -16,6 +16,8 @@ ERR_NULL, ERR_SHAPE, ERR_BITS, ERR_BATCH, ERR_CUDA, ERR_NO_DEVICE, ERR_TOO_LARGE
 SYMBOLS = (
     "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
     "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matvec_static_scratch", "lutgemm_dequantize",
+    "lutgemm_matvec_tp", "lutgemm_matvec_tiles", "lutgemm_tp_finalize",
+    "lutgemm_ipc_alloc", "lutgemm_ipc_open", "lutgemm_ipc_close", "lutgemm_ipc_free",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
@@ -27,6 +29,13 @@ class WeightDesc(C.Structure):
     _fields_ = [("bWeight", C.c_void_p), ("alpha", C.c_void_p), ("q_bias", C.c_void_p),
                 ("num_groups", C.c_int), ("group_size", C.c_int), ("mSize", C.c_int), ("kSize", C.c_int),
                 ("nb", C.c_int), ("is_row_wise_quantize", C.c_int), ("device", C.c_int)]
+
+
+class TpLink(C.Structure):
+    _fields_ = [("x_mode", C.c_int), ("out_mode", C.c_int), ("world", C.c_int), ("out_off", C.c_int),
+                ("x_slots", C.c_void_p), ("x_slot_stride", C.c_int), ("x_off", C.c_int),
+                ("flag_in", C.c_void_p), ("flag_target", C.c_uint), ("done_counter", C.c_void_p),
+                ("out16", C.c_void_p * 8), ("out32", C.c_void_p * 8), ("flag_out", C.c_void_p * 8)]
 
 
 class LutGemmError(RuntimeError):
@@ -63,6 +72,13 @@ def lib():
     L.lutgemm_matmul_host.argtypes = [vp, vp, vp, ip]
     L.lutgemm_matvec_static_scratch.argtypes = [vp, vp, vp, vp, vp, ip, ip, ip, ip, vp]
     L.lutgemm_dequantize.argtypes = [vp, vp, vp]
+    L.lutgemm_matvec_tp.argtypes = [vp, vp, C.POINTER(TpLink), vp, vp, vp]
+    L.lutgemm_matvec_tiles.argtypes = [vp, C.POINTER(ip)]
+    L.lutgemm_tp_finalize.argtypes = [vp, vp, vp, ip, ip, ip, vp, C.c_uint, vp, vp]
+    L.lutgemm_ipc_alloc.argtypes = [C.c_size_t, C.POINTER(vp), vp]
+    L.lutgemm_ipc_open.argtypes = [vp, C.POINTER(vp)]
+    L.lutgemm_ipc_close.argtypes = [vp]
+    L.lutgemm_ipc_free.argtypes = [vp]
     L.lutgemm_pack_planes.argtypes = [vp, ip, ip, ip, vp]
     L.lutgemm_pack_planes_device.argtypes = [vp, ip, ip, ip, vp, vp]
     L.lutgemm_uniform_to_bcq.argtypes = [vp, vp, vp, ip, ip, ip, ip, vp, vp, vp]

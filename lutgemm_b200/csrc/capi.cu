@@ -211,6 +211,30 @@ int launch_gemv_q(const lg::GemvParams& p, dim3 grid, bool bias, cudaStream_t st
     return LUTGEMM_OK;
 }
 
+// Grid of the TMA-fed matvec for a container: columns per CTA and the number of column tiles.
+void gemv_tma_geometry(const lutgemm_weight* w, int* nslabs, int* n_tile, int* tiles) {
+    *nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
+    *n_tile = choose_ntile(w->N, *nslabs, 1, lg::kStageCols);
+    *tiles = (w->N + *n_tile - 1) / *n_tile;
+}
+
+int launch_gemv_tma_any(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, const lg::TpLink* link,
+                        cudaStream_t st) {
+    lg::Gemv2Params p2 = {};
+    p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
+    p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
+    p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
+    int tiles = 0;
+    gemv_tma_geometry(w, &p2.nslabs, &p2.n_tile, &tiles);
+    p2.a_rows = w->a_rows;
+    p2.ordered = g_ordered.load();
+    if (link) p2.tp = *link;
+    dim3 grid2(tiles, p2.nslabs);
+    const bool bias2 = w->q_bias != nullptr;
+    if (w->g % 128 == 0) return launch_gemv_tma<2>(w, p2, grid2, bias2, st);
+    return launch_gemv_tma<1>(w, p2, grid2, bias2, st);
+}
+
 // One matvec row: y (fp16 and/or fp32) = x . W
 int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
     const bool use_tma = (g_variant.load() == 0) && w->tma_ok;
@@ -223,7 +247,7 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
         return LUTGEMM_OK;
     }
     if (use_tma) {
-        lg::Gemv2Params p2;
+        lg::Gemv2Params p2 = {};
         p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
         p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
         p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
@@ -557,7 +581,7 @@ int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uin
     LG_CUDA(cudaMemsetAsync(scratch, 0, (size_t)N * sizeof(float), st));
     LG_CUDA(cudaMemsetAsync(scratch + kStaticRowBytes, 0, (size_t)tiles * sizeof(unsigned), st));
     LG_CUDA(cudaMemsetAsync(scratch + kStaticRowBytes + kStaticCounterBytes, 0, sizeof(int), st));
-    lg::Gemv2Params p;
+    lg::Gemv2Params p = {};
     p.bW = w.bW; p.alpha = w.alpha; p.q_bias = w.q_bias; p.x = (const __half*)in_fp16;
     p.partial = (float*)scratch;
     p.counters = (unsigned*)(scratch + kStaticRowBytes);
@@ -570,6 +594,83 @@ int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uin
     const bool bias = d_q_bias_fp16 != nullptr;
     if (w.g % 128 == 0) return launch_gemv_tma<2>(&w, p, grid, bias, st);
     return launch_gemv_tma<1>(&w, p, grid, bias, st);
+}
+
+int lutgemm_matvec_tiles(lutgemm_weight_t w, int* tiles) {
+    if (!w || !tiles) return LUTGEMM_ERR_NULL;
+    if (!w->tma_ok) return LUTGEMM_ERR_SHAPE;
+    int nslabs = 0, n_tile = 0;
+    gemv_tma_geometry(w, &nslabs, &n_tile, tiles);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_matvec_tp(const void* in_fp16, lutgemm_weight_t w, const lutgemm_tp_link* link, void* out_fp16,
+                      float* out_f32, void* stream) {
+    if (!w || !link) return LUTGEMM_ERR_NULL;
+    if (!w->tma_ok) return LUTGEMM_ERR_SHAPE;
+    if (link->world < 1 || link->world > 8 || link->x_mode < 0 || link->x_mode > 2 || link->out_mode < 0 || link->out_mode > 2)
+        return LUTGEMM_ERR_SHAPE;
+    if (link->x_mode != 2 && !in_fp16) return LUTGEMM_ERR_NULL;
+    if (link->x_mode == 2 && (!link->x_slots || (link->x_off % 8) || (link->x_slot_stride % 4))) return LUTGEMM_ERR_ALIGN;
+    if (link->x_mode != 0 && (!link->flag_in || !link->done_counter)) return LUTGEMM_ERR_NULL;
+    if (link->out_mode == 0 && !out_fp16 && !out_f32) return LUTGEMM_ERR_NULL;
+    if (((uintptr_t)in_fp16 & 15) || ((uintptr_t)out_fp16 & 15) || ((uintptr_t)out_f32 & 15)) return LUTGEMM_ERR_ALIGN;
+    lg::TpLink t = {};
+    t.x_mode = link->x_mode; t.out_mode = link->out_mode; t.world = link->world; t.out_off = link->out_off;
+    t.x_slots = link->x_slots; t.x_slot_stride = link->x_slot_stride; t.x_off = link->x_off;
+    t.flag_in = link->flag_in; t.flag_target = link->flag_target; t.done_counter = link->done_counter;
+    for (int r = 0; r < link->world; r++) {
+        if (link->out_mode == 1 && (!link->out16[r] || ((uintptr_t)link->out16[r] & 15) || (link->out_off % 8))) return LUTGEMM_ERR_ALIGN;
+        if (link->out_mode == 2 && (!link->out32[r] || ((uintptr_t)link->out32[r] & 15))) return LUTGEMM_ERR_ALIGN;
+        if (link->out_mode != 0 && !link->flag_out[r]) return LUTGEMM_ERR_NULL;
+        t.out16[r] = (__half*)link->out16[r]; t.out32[r] = link->out32[r]; t.flag_out[r] = link->flag_out[r];
+    }
+    return launch_gemv_tma_any(w, (const __half*)in_fp16, (__half*)out_fp16, out_f32, &t, (cudaStream_t)stream);
+}
+
+int lutgemm_tp_finalize(void* out_fp16, float* out_f32, const float* slots, int slot_stride, int world, int n,
+                        unsigned* flag_in, unsigned flag_target, lutgemm_weight_t status_owner, void* stream) {
+    if ((!out_fp16 && !out_f32) || !slots || !flag_in || !status_owner) return LUTGEMM_ERR_NULL;
+    if (world < 1 || world > 8 || n < 1) return LUTGEMM_ERR_SHAPE;
+    lg::tp_finalize_kernel<<<1, 256, 0, (cudaStream_t)stream>>>((__half*)out_fp16, out_f32, slots, slot_stride, world, n,
+                                                                 flag_in, flag_target, status_owner->status);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_ipc_alloc(size_t bytes, void** dptr, void* handle64) {
+    if (!dptr || !handle64 || bytes == 0) return LUTGEMM_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    LG_CUDA(cudaMalloc(&p, bytes));
+    LG_CUDA(cudaMemset(p, 0, bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { g_last_cuda = (int)e; cudaFree(p); return LUTGEMM_ERR_CUDA; }
+    std::memcpy(handle64, &h, 64);
+    *dptr = p;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_ipc_open(const void* handle64, void** dptr) {
+    if (!handle64 || !dptr) return LUTGEMM_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    LG_CUDA(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_ipc_close(void* dptr) {
+    if (!dptr) return LUTGEMM_OK;
+    LG_CUDA(cudaIpcCloseMemHandle(dptr));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_ipc_free(void* dptr) {
+    if (!dptr) return LUTGEMM_OK;
+    LG_CUDA(cudaFree(dptr));
+    return LUTGEMM_OK;
 }
 
 int lutgemm_dequantize(lutgemm_weight_t w, void* d_fW, void* stream) {

@@ -69,7 +69,49 @@ __host__ __device__ constexpr int gemv2_smem_bytes(int a_rows) {
     return kStage0Off + gemv2_num_stages(a_rows) * gemv2_stage_bytes(a_rows);
 }
 
-enum { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusConsumerTimeout = 2 };
+enum { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusConsumerTimeout = 2, kStatusPeerTimeout = 4 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for a flag that other GPUs increment (about a quarter of a second at most).
+__device__ __forceinline__ bool wait_flag_bounded(const unsigned* flag, unsigned target) {
+    for (unsigned it = 0; it < (1u << 18); it++) {
+        if (ld_acquire_sys(flag) >= target) return true;
+        if (it > 16) __nanosleep(200);
+    }
+    return false;
+}
+
+// Tensor-parallel links of one matvec (all zero / null for an ordinary call).
+//  Input side:  x_mode 0: p.x is ready when the previous kernel of the stream has finished;
+//               x_mode 1: p.x is an fp16 vector in THIS GPU's memory that every rank fills by peer stores
+//                         (all-gather); wait until flag_in reaches flag_target;
+//               x_mode 2: the activations are the sum, in rank order, of `world` fp32 rows
+//                         x_slots[r * x_slot_stride + x_off + k] written by the ranks (all-reduce), rounded to
+//                         fp16 once; wait as above.
+//  Output side: out_mode 0: p.y16 / p.y32 in local memory;
+//               out_mode 1: the fp16 result goes to out16[r] + out_off on every rank r (peer-mapped pointers);
+//               out_mode 2: the fp32 result goes to out32[r] (this rank's slot on rank r);
+//               then flag_out[r] is incremented once per finished column tile, release at system scope.
+//  The last CTA to pass the input wait resets flag_in, so the same words serve the next step (CUDA graphs
+//  replay constant parameters).  All waits are bounded.
+struct TpLink {
+    int x_mode, out_mode, world, out_off;
+    const float* x_slots;
+    int x_slot_stride, x_off;
+    unsigned* flag_in;
+    unsigned flag_target;
+    unsigned* done_counter;
+    __half* out16[8];
+    float* out32[8];
+    unsigned* flag_out[8];
+};
 
 struct Gemv2Params {
     const uint32_t* bW;      // [K/32][q][N]
@@ -86,6 +128,7 @@ struct Gemv2Params {
     int nslabs;              // gridDim.y
     int a_rows;              // alpha groups per slab (rows of the alpha box): max(1, 512 / g)
     int ordered;             // 1: slabs are added in slab order (bit-reproducible); 0: fp32 reductions in L2
+    TpLink tp;
 };
 
 __device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
@@ -137,14 +180,27 @@ __device__ __forceinline__ float2 lookup_word(const unsigned char* lut, uint32_t
 // Table for the 64 chunks of one slab.  Consumer thread t owns slot (t & 63) and the 32 entries
 // idx in [32 (t >> 6), +32), walked in Gray-code order (one add per entry).  A warp stores 32
 // consecutive slots of one idx row: conflict free.
-__device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, int k0, int K, int ctid) {
+__device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, int k0, int K, int ctid, const TpLink& tp) {
     const int slot = ctid & 63, part = ctid >> 6;
     const int u = slot >> 5, G = (slot >> 3) & 3, jp = (slot >> 2) & 1, beta = slot & 3;
     const int chunk = 4 * (4 * G + jp + 2 * u) + beta;       // 8-activation chunk in natural k order
     float xv[8];
-    {
+    if (tp.x_mode == 2) {
+        // all-reduced input: add the ranks' fp32 rows in rank order, round to fp16 once
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (k0 + 8 * chunk < K) {
+            for (int r = 0; r < tp.world; r++) {
+                const float4* src = reinterpret_cast<const float4*>(tp.x_slots + (size_t)r * tp.x_slot_stride + tp.x_off + k0 + 8 * chunk);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; t++) xv[t] = __half2float(__float2half_rn(acc[t]));
+    } else {
         uint4 raw = make_uint4(0, 0, 0, 0);
-        if (k0 + 8 * chunk < K) raw = *reinterpret_cast<const uint4*>(x + k0 + 8 * chunk);
+        if (k0 + 8 * chunk < K) raw = __ldcg(reinterpret_cast<const uint4*>(x + k0 + 8 * chunk));
         const float2 f0 = half2_bits_to_float2(raw.x), f1 = half2_bits_to_float2(raw.y);
         const float2 f2 = half2_bits_to_float2(raw.z), f3 = half2_bits_to_float2(raw.w);
         xv[0] = f0.x; xv[1] = f0.y; xv[2] = f1.x; xv[3] = f1.y; xv[4] = f2.x; xv[5] = f2.y; xv[6] = f3.x; xv[7] = f3.y;
@@ -234,7 +290,19 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int cb = warp & 7, h = warp >> 3;
         const int jp = (c8 & 1) ^ h;             // this lane's words in the slab: kw = 4 rr + jp + 2 u, u = 0, 1
         pdl_wait_prior_grids();                  // the activations may come from the previous kernel
-        build_lut2(lut, p.x, k0, p.K, tid);
+        if (p.tp.x_mode != 0) {
+            // ... or from the other GPUs: wait for their pushes (bounded), then let the last CTA re-arm the flag
+            if (tid == 0) {
+                if (!wait_flag_bounded(p.tp.flag_in, p.tp.flag_target)) atomicExch(p.status, kStatusPeerTimeout);
+                const unsigned prev = atomicAdd(p.tp.done_counter, 1u);
+                if (prev == gridDim.x * gridDim.y - 1u) {
+                    *reinterpret_cast<volatile unsigned*>(p.tp.flag_in) = 0u;
+                    *reinterpret_cast<volatile unsigned*>(p.tp.done_counter) = 0u;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+        }
+        build_lut2(lut, p.x, k0, p.K, tid, p.tp);
         asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
 
         uint32_t cs = 0, sel[4];
@@ -389,16 +457,47 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sl * rowN));
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        if (p.y32) *reinterpret_cast<float4*>(p.y32 + c) = s;
-        if (p.y16) {
-            __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
-            uint2 o;
-            o.x = *reinterpret_cast<uint32_t*>(&lo);
-            o.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(p.y16 + c) = o;
+        __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        if (p.tp.out_mode == 0) {
+            if (p.y32) *reinterpret_cast<float4*>(p.y32 + c) = s;
+            if (p.y16) *reinterpret_cast<uint2*>(p.y16 + c) = o;
+        } else if (p.tp.out_mode == 1) {
+            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<uint2*>(p.tp.out16[r] + p.tp.out_off + c) = o;   // peer stores
+        } else {
+            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<float4*>(p.tp.out32[r] + c) = s;                  // peer stores
         }
     }
+    if (p.tp.out_mode != 0) {
+        // publish this tile to every rank: data first (system-scope fence by every storing thread), then the flag
+        __threadfence_system();
+        __syncthreads();
+        if (tid < p.tp.world) red_release_sys_add(p.tp.flag_out[tid], 1u);
+    }
     if (tid == 0) p.counters[blockIdx.x] = 0u;   // ready for the next launch on this stream
+}
+
+// Last consumer of a tensor-parallel chain: waits for the ranks' fp32 rows, adds them in rank order and writes
+// the fp16 (and optionally fp32) vector; re-arms the flag.  One CTA.
+__global__ void __launch_bounds__(256)
+tp_finalize_kernel(__half* y16, float* y32, const float* slots, int slot_stride, int world, int n,
+                   unsigned* flag_in, unsigned flag_target, int* status) {
+    __shared__ int s_ok;
+    pdl_wait_prior_grids();
+    if (threadIdx.x == 0) {
+        s_ok = wait_flag_bounded(flag_in, flag_target) ? 1 : 0;
+        if (!s_ok) atomicExch(status, kStatusPeerTimeout);
+        *reinterpret_cast<volatile unsigned*>(flag_in) = 0u;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < world; r++) acc += __ldcg(slots + (size_t)r * slot_stride + i);
+        if (y32) y32[i] = acc;
+        if (y16) y16[i] = __float2half_rn(acc);
+    }
 }
 
 }  // namespace lg

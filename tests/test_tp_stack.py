@@ -114,3 +114,35 @@ def test_single_gpu_stack_matches_host_chain():
         cur = outs["fc2"]
     ref = cur.astype(np.float32).reshape(-1)
     assert np.abs(y - ref).max() <= 1e-2 * np.abs(ref).max() + 1e-3
+
+
+@pytest.mark.gpu
+def test_fused_stack_single_rank_matches_collective_stack_and_replays():
+    """world = 1 exercises the whole fused machinery (peer stores to itself, flags, re-arming, graph replay)."""
+    torch = pytest.importorskip("torch")
+    from lutgemm_b200 import tp_fused
+    H, F, Q, G, LAYERS = 512, 1024, 3, 128, 3
+    plain = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, device="cuda", seed=1, generate="host")
+    fused = tp_fused.FusedTPStack(H, F, Q, G, LAYERS, device="cuda", seed=1, generate="host")
+    x = torch.from_numpy(synth.activations(1, H, seed=4).view(np.int16)).cuda().view(torch.float16).reshape(-1)
+    want = plain.step(x).float().cpu().numpy()
+    for rep in range(3):                                   # the flags must re-arm themselves between steps
+        got = fused.step(x).float().cpu().numpy()
+        assert fused.device_status() == 0
+        assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max() + 1e-4, rep
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fused.step(x)
+        with torch.cuda.graph(g, stream=side):
+            fused.step(x)
+    torch.cuda.current_stream().wait_stream(side)
+    for rep in range(3):
+        g.replay()
+        torch.cuda.synchronize()
+        got = fused._y16.float().cpu().numpy()
+        assert fused.device_status() == 0
+        assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max() + 1e-4, rep
+    del g
+    fused.close()
