@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack"],
                     help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more")
+    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
+                    help="stack workload: exchange steps fused into the matvec kernels (peer pushes) or NCCL collectives")
     ap.add_argument("--layers", type=int, default=96, help="decoder layers of the stack workload")
     ap.add_argument("--hidden", type=int, default=12288)
     ap.add_argument("--ffn", type=int, default=49152)
@@ -230,7 +232,11 @@ def run_stack(a):
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     lib = capi.lib()
     lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
-    stack = tp_stack.TPLinearStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    if a.tp == "fused":
+        from lutgemm_b200 import tp_fused
+        stack = tp_fused.FusedTPStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    else:
+        stack = tp_stack.TPLinearStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
     B = tp_stack.stack_algorithmic_bytes(a.hidden, a.ffn, a.q, a.g, a.layers)
     x_host = synth.activations(1, a.hidden, seed=5).reshape(-1)
     x = torch.from_numpy(x_host.view(np.int16).copy()).cuda().view(torch.float16)
@@ -304,13 +310,14 @@ def run_stack(a):
             "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"tensor-parallel decoder linear stack, {a.layers} layers, hidden {a.hidden}, ffn {a.ffn}, "
-                                   f"q={a.q} g={a.g} m=1", "parallelism": f"tp{world}: QKV/FC1 column-parallel + all-gather, "
-                                   "out-proj/FC2 row-parallel + all-reduce (NCCL)", "algorithmic_bytes_per_step": B,
+                                   f"q={a.q} g={a.g} m=1", "parallelism": f"tp{world}: QKV/FC1 column-parallel + all-gather, out-proj/FC2 row-parallel + all-reduce; "
+                                   + ("exchange fused into the matvec kernels (peer stores + flags over NVLink)" if a.tp == "fused"
+                                      else "NCCL collectives"), "algorithmic_bytes_per_step": B,
                        "l2": f"{B / world / 1e9:.1f} GB of packed weights per GPU per step, far larger than L2",
                        "launch": "python" if graph is None else "cuda graph of one step, replayed"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_source": peak_kind, "traffic": None, "kernel": "gemv_tma_kernel (per GPU average over the step, collectives included)"},
-            "gpu_launches": int(a.steps * a.layers * 4),
+            "gpu_launches": int(a.steps * (a.layers * 4 + (1 if a.tp == "fused" else 0))),
             "clocks": clocks,
             "e2e": {"value": B * a.steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * a.hidden, "d2h_bytes_per_step": 2 * a.hidden},
         }

@@ -304,14 +304,11 @@ int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, in
     if (!enc) return LUTGEMM_ERR_CUDA;
     lg::TcParams p;
     p.m = m;
-    p.m_pad = (m + 15) / 16 * 16;
-    p.tmem_cols = 32;
-    while (p.tmem_cols < p.m_pad) p.tmem_cols *= 2;
     CUtensorMap tmX;
     {
         cuuint64_t dims[2] = {(cuuint64_t)w->K, (cuuint64_t)m};
         cuuint64_t strides[1] = {(cuuint64_t)w->K * 2};
-        cuuint32_t box[2] = {64, (cuuint32_t)p.m_pad};
+        cuuint32_t box[2] = {64, (cuuint32_t)lg::kTcTileM};
         cuuint32_t es[2] = {1, 1};
         if (enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, es,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

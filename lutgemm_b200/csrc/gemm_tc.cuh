@@ -5,15 +5,18 @@
 // lutGEMM/src/cuda/kernels/dequant_fp16.hpp:54-107, lutGEMM/src/cuda/kernels/cublas.h:47-55).  Here the
 // dense values never leave the SM:
 //
-//   CTA = 128 output columns (the MMA M dimension: "swap-AB", weights are operand A) x a k-range.
-//   16 expansion warps turn ONE bit plane at a time into a dense fp16 tile A_b[n][k] = +-alpha_b
-//   (128 x 128, K-major, 128-byte swizzle) in shared memory, the sign applied by XOR-ing the fp16
+//   CTA = 256 output columns x a k-range.  The weights are the MMA's N-side operand (N = 256, the widest
+//   instruction: a tcgen05.mma costs about the same time whatever its N, so wide N is what keeps the
+//   tensor pipe from being the limit at small batch), the activations the M-side operand (M = 128 rows,
+//   rows beyond m zero-filled by TMA).
+//   16 expansion warps turn ONE bit plane at a time into a dense fp16 tile B_b[n][k] = +-alpha_b
+//   (256 x 64, K-major, 128-byte swizzle) in shared memory, the sign applied by XOR-ing the fp16
 //   sign bits of two weights at a time, so every operand value is exact; q_bias is one more "plane"
 //   whose tile holds q_bias[g][n] unsigned.  All planes accumulate into the same fp32 accumulator:
 //   y = sum_k x (sum_b A_b + q_bias) with exact products and fp32 sums, the accuracy of the matvec path;
-//   one lane loads the matching activation tiles x[m][k] with tiled TMA (128-byte swizzle, rows
-//   beyond m zero-filled); one lane issues tcgen05.mma (kind::f16, M = 128, N = m padded to 16,
-//   K = 16 per instruction) accumulating fp32 in tensor memory over the whole k-range;
+//   one lane loads the matching activation tiles x[m][k] with tiled TMA (128-byte swizzle);
+//   one lane issues tcgen05.mma (kind::f16, M = 128, N = 256, K = 16 per instruction) accumulating
+//   fp32 in tensor memory (128 lanes x 256 columns) over the whole k-range;
 //   tcgen05.commit releases each shared-memory stage and finally hands the accumulator to four
 //   epilogue warps, which read it with tcgen05.ld and either store fp16/fp32 outputs directly or, with
 //   split-k, add their partial sums with fp32 reductions in L2 into a workspace that the last CTA of
@@ -31,14 +34,16 @@
 
 namespace lg {
 
-constexpr int kTcTileN = 128;                 // output columns per CTA (MMA M)
-constexpr int kTcTileK = 128;                 // k per stage: two 64-k swizzle atoms
+constexpr int kTcTileN = 256;                 // output columns per CTA (MMA N)
+constexpr int kTcTileK = 64;                  // k per stage: one 64-k swizzle atom
+constexpr int kTcTileM = 128;                 // activation rows per MMA (zero padded)
 constexpr int kTcStages = 3;
 constexpr int kTcExpWarps = 16;
 constexpr int kTcThreads = (kTcExpWarps + 2) * 32;       // + TMA warp + MMA warp = 576
-constexpr int kTcAStageBytes = kTcTileN * kTcTileK * 2;   // 32768: [2 halves][128 rows][128 B]
-constexpr int kTcBRingBytes = 98304;                     // activation ring: one slot per k tile, [2 halves][m_pad rows][128 B]
-constexpr int kTcBSlotsMax = 8;
+constexpr int kTcAStageBytes = kTcTileN * kTcTileK * 2;   // 32768: weight tile [256 rows][128 B]
+constexpr int kTcBRingBytes = 98304;                     // activation ring: one slot per k tile, [128 rows][128 B]
+constexpr int kTcBSlotBytes = kTcTileM * kTcTileK * 2;   // 16384
+constexpr int kTcBSlotsMax = kTcBRingBytes / kTcBSlotBytes;   // 6
 constexpr int kTcBarOff = kTcStages * kTcAStageBytes + kTcBRingBytes;   // 98304 + 98304
 constexpr int kTcSmemBytes = kTcBarOff + 256;
 
@@ -54,9 +59,8 @@ struct TcParams {
     __half* y16;             // [m][N] or nullptr
     float* y32;              // [m][N] or nullptr
     int N, K, q, g;
-    int m, m_pad;            // rows, rows padded to a multiple of 16 (<= 128)
-    int ktiles_per_cta;      // 128-k tiles per CTA (split-k along gridDim.y)
-    int tmem_cols;           // power of two >= max(32, m_pad)
+    int m;                   // rows (<= 128)
+    int ktiles_per_cta;      // 64-k tiles per CTA (split-k along gridDim.y)
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
@@ -111,8 +115,9 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
 __device__ __forceinline__ uint32_t umma_idesc_f16_f32(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
+constexpr uint32_t kTcTmemCols = 256;         // fp32 accumulator: 128 lanes x 256 columns
 
-// Q: number of bit planes; BIAS: container has q_bias.  tmX: 2-D map {K, m} of fp16, box {64, m_pad}, 128-byte swizzle.
+// Q: number of bit planes; BIAS: container has q_bias.  tmX: 2-D map {K, m} of fp16, box {64, 128}, 128-byte swizzle.
 template <int Q, bool BIAS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
@@ -139,10 +144,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     constexpr int planes = Q + (BIAS ? 1 : 0);            // q_bias rides as one more plane
     const int nst = nkt * planes;                         // pipeline stages: (k tile, plane) pairs
     const size_t rowN = (size_t)N;
-    const uint32_t b_half_bytes = (uint32_t)p.m_pad * 128u;
-    const uint32_t b_slot_bytes = 2u * b_half_bytes;
-    int nb_slots = kTcBRingBytes / (int)b_slot_bytes;          // 3 (m_pad = 128) .. 8
-    if (nb_slots > kTcBSlotsMax) nb_slots = kTcBSlotsMax;
+    constexpr uint32_t b_slot_bytes = kTcBSlotBytes;
+    constexpr int nb_slots = kTcBSlotsMax;
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; s++) {
@@ -157,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
         mbar_fence_init();
     }
     if (warp == kTcExpWarps + 1) {          // the MMA warp owns the tensor-memory allocation
-        tmem_alloc(smem_u32(s_tmem), (uint32_t)p.tmem_cols);
+        tmem_alloc(smem_u32(s_tmem), kTcTmemCols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -168,13 +171,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
 
     if (warp < kTcExpWarps) {
         // ---------------- expansion: packed planes -> dense fp16 tile in shared memory ----------------
-        const int rq = warp & 3, ks = warp >> 2;          // row quarter (32 rows), k-word slot (0..3) of the tile
-        const int row = rq * 32 + lane;                   // row of the tile = output column n0 + row
+        const int ks = warp >> 3;                         // which of the tile's two packed k-words
+        const int row = (warp & 7) * 32 + lane;           // row of the tile = output column n0 + row
         const int n = n0 + row;
         const bool n_ok = n < N;
-        // swizzled position of this thread's four 16-byte chunks: half = ks >> 1, chunks 4 (ks & 1) .. +3
-        const uint32_t row_off = (uint32_t)(ks >> 1) * (kTcTileN * 128) + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
-        const int c0 = 4 * (ks & 1);
+        // swizzled position of this thread's four 16-byte chunks (4 ks .. 4 ks + 3 of the 128-byte row)
+        const uint32_t row_off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+        const int c0 = 4 * ks;
         // One k tile = `planes` pipeline stages.  The packed words and scales of a k tile are fetched two
         // tiles ahead into registers (a tile is far shorter than a trip to HBM); plane indices are
         // compile-time, addresses advance by constant strides.
@@ -270,14 +273,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
                 const uint32_t dst = b_base + slot * b_slot_bytes;
                 mbar_arrive_expect_tx(bar_bfull + 8 * slot, b_slot_bytes);
                 tma_load_2d(dst, &tmX, k, 0, bar_bfull + 8 * slot);
-                tma_load_2d(dst + b_half_bytes, &tmX, k + 64, 0, bar_bfull + 8 * slot);
                 if (++slot == nb_slots) { slot = 0; round++; }
             }
         }
     } else {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16_f32(p.m_pad);
+            const uint32_t idesc = umma_idesc_f16_f32(kTcTileN);
             int s = 0, sround = 0, bslot = 0, bround = 0;
             for (int j = 0; j < nkt && !timed_out; j++) {
                 if (!mbar_wait_bounded(bar_bfull + 8 * bslot, bround & 1)) { timed_out = true; break; }
@@ -285,13 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
                     if (!mbar_wait_bounded(bar_afull + 8 * s, sround & 1)) { timed_out = true; break; }
                     tc_fence_after_sync();
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-#pragma unroll
-                        for (int k16 = 0; k16 < 4; k16++) {
-                            const uint64_t da = umma_desc_k_sw128(a_base + s * kTcAStageBytes + half * (kTcTileN * 128) + k16 * 32);
-                            const uint64_t db = umma_desc_k_sw128(b_base + bslot * b_slot_bytes + half * b_half_bytes + k16 * 32);
-                            umma_f16_ss(tmem_acc, da, db, idesc, (j > 0 || b > 0 || half > 0 || k16 > 0) ? 1u : 0u);
-                        }
+                    for (int k16 = 0; k16 < 4; k16++) {
+                        // M-side operand: activations; N-side operand: this plane's +-alpha tile
+                        const uint64_t dx = umma_desc_k_sw128(b_base + bslot * b_slot_bytes + k16 * 32);
+                        const uint64_t dw = umma_desc_k_sw128(a_base + s * kTcAStageBytes + k16 * 32);
+                        umma_f16_ss(tmem_acc, dx, dw, idesc, (j > 0 || b > 0 || k16 > 0) ? 1u : 0u);
                     }
                     umma_commit(bar_empty + 8 * s);        // weight stage reusable once these MMAs have read it
                     if (++s == kTcStages) { s = 0; sround++; }
@@ -304,33 +304,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     }
     if (timed_out) atomicExch(p.status, kStatusTcTimeout);
 
-    // ---------------- epilogue: warps 0..3 read the accumulator (TMEM lanes 32 w .. 32 w + 31) ----------------
+    // ---------------- epilogue: warps 0..3 read the accumulator (TMEM lane = activation row, column = output column) ----
     if (warp < 4) {
         bool ok = (nst > 0) && mbar_wait_bounded(bar_acc, 0);
         if (!ok && nst > 0) atomicExch(p.status, kStatusTcTimeout);
         tc_fence_after_sync();
-        const int n = n0 + warp * 32 + lane;
+        const int mrow = warp * 32 + lane;
         const bool split = gridDim.y > 1;
-        for (int mc = 0; mc < p.m_pad; mc += 16) {
-            uint32_t r[16];
-            if (ok) {
-                tmem_ld_x16(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)mc, r);
-                tmem_ld_wait();
-            } else {
+        if (warp * 32 < p.m) {                              // warp-uniform: this quadrant holds real rows
+            for (int nc = 0; nc < kTcTileN; nc += 16) {
+                uint32_t r[16];
+                if (ok) {
+                    tmem_ld_x16(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)nc, r);
+                    tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = 0u;
-            }
-            if (n < N) {
+                    for (int j = 0; j < 16; j++) r[j] = 0u;
+                }
+                if (mrow < p.m) {
+                    const size_t base = (size_t)mrow * rowN + n0 + nc;
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int mrow = mc + j;
-                    if (mrow < p.m) {
-                        const float v = __uint_as_float(r[j]);
-                        if (split) {
-                            atomicAdd(p.partial + (size_t)mrow * rowN + n, v);
-                        } else {
-                            if (p.y32) p.y32[(size_t)mrow * rowN + n] = v;
-                            if (p.y16) p.y16[(size_t)mrow * rowN + n] = __float2half_rn(v);
+                    for (int j = 0; j < 16; j++) {
+                        if (n0 + nc + j < N) {
+                            const float v = __uint_as_float(r[j]);
+                            if (split) {
+                                atomicAdd(p.partial + base + j, v);
+                            } else {
+                                if (p.y32) p.y32[base + j] = v;
+                                if (p.y16) p.y16[base + j] = __float2half_rn(v);
+                            }
                         }
                     }
                 }
@@ -342,7 +344,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     __syncthreads();
     if (warp == kTcExpWarps + 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_acc, (uint32_t)p.tmem_cols);
+        tmem_dealloc(tmem_acc, kTcTmemCols);
     }
     if (gridDim.y == 1) return;
 

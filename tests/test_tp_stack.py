@@ -146,3 +146,16 @@ def test_fused_stack_single_rank_matches_collective_stack_and_replays():
         assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max() + 1e-4, rep
     del g
     fused.close()
+
+
+@pytest.mark.gpu
+def test_fused_stack_two_gpus_matches_nccl_stack():
+    torch = pytest.importorskip("torch")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "tests", "tp_worker.py")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    lines = [l for l in out.stdout.splitlines() if l.startswith("TPRESULT")]
+    assert out.returncode == 0 and len(lines) == 2 and all("ok=True" in l for l in lines), out.stdout[-2000:] + out.stderr[-2000:]
