@@ -148,21 +148,35 @@ int sm_count() {
     return sms;
 }
 
-// Columns per CTA: enough CTAs to occupy every SM (`per_sm` CTAs each), but wide enough that
-// building the table stays a small part of a CTA's work.  Rounded to `quantum` columns.
+// Columns per CTA (a multiple of `quantum`).  Every CTA rebuilds its table, so wide tiles are cheaper, but the
+// grid should fill whole waves of `per_sm` CTAs per SM: among the candidate widths the widest one whose wave
+// efficiency is within 5 % of the best is taken.
 int choose_ntile(int N, int nslabs, int per_sm, int quantum) {
     int forced = g_ntile_override.load();
     int ntile;
     if (forced > 0) {
-        ntile = forced;
+        ntile = (forced + quantum - 1) / quantum * quantum;
     } else {
         const int slots = per_sm * sm_count();
-        int tiles = slots / nslabs;
-        if (tiles < 1) tiles = 1;
-        ntile = (N + tiles - 1) / tiles;
-        if (ntile < 512) ntile = 512;
+        const int n_max = (N + quantum - 1) / quantum * quantum;
+        int lo = quantum;
+        if (lo > n_max) lo = n_max;
+        double best = 0.0;
+        for (int t = lo; t <= n_max; t += quantum) {
+            const long long ctas = (long long)((N + t - 1) / t) * nslabs;
+            const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+            if (eff > best) best = eff;
+        }
+        ntile = lo;
+        for (int t = lo; t <= n_max; t += quantum) {
+            const long long ctas = (long long)((N + t - 1) / t) * nslabs;
+            const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+            if (eff >= 0.95 * best) ntile = t;      // keeps the widest qualifying tile
+        }
+        // same number of tiles, equal widths
+        const int tiles = (N + ntile - 1) / ntile;
+        ntile = ((N + tiles - 1) / tiles + quantum - 1) / quantum * quantum;
     }
-    ntile = (ntile + quantum - 1) / quantum * quantum;
     while ((N + ntile - 1) / ntile > kMaxCounters) ntile *= 2;
     return ntile;
 }
