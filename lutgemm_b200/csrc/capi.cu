@@ -341,6 +341,7 @@ int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, in
         if (eff > best + 0.02) { best = eff; splitk = c; }
     }
     p.ktiles_per_cta = (kt_total + splitk - 1) / splitk;
+    p.ktiles_per_cta += p.ktiles_per_cta & 1;            // a pipeline stage holds a pair of 64-k sub-tiles
     splitk = (kt_total + p.ktiles_per_cta - 1) / p.ktiles_per_cta;
     if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
     if (splitk > 1 && w->tc_rows < m) {

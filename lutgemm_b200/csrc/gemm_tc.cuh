@@ -35,12 +35,13 @@
 namespace lg {
 
 constexpr int kTcTileN = 256;                 // output columns per CTA (MMA N)
-constexpr int kTcTileK = 64;                  // k per stage: one 64-k swizzle atom
+constexpr int kTcTileK = 64;                  // k per sub-tile: one 64-k swizzle atom; a pipeline stage holds two
 constexpr int kTcTileM = 128;                 // activation rows per MMA (zero padded)
-constexpr int kTcStages = 3;
+constexpr int kTcStages = 2;
 constexpr int kTcExpWarps = 16;
 constexpr int kTcThreads = (kTcExpWarps + 2) * 32;       // + TMA warp + MMA warp = 576
-constexpr int kTcAStageBytes = kTcTileN * kTcTileK * 2;   // 32768: weight tile [256 rows][128 B]
+constexpr int kTcASubBytes = kTcTileN * kTcTileK * 2;     // 32768: weight sub-tile [256 rows][128 B]
+constexpr int kTcAStageBytes = 2 * kTcASubBytes;          // 65536: two sub-tiles = 128 k per stage
 constexpr int kTcBRingBytes = 98304;                     // activation ring: one slot per k tile, [128 rows][128 B]
 constexpr int kTcBSlotBytes = kTcTileM * kTcTileK * 2;   // 16384
 constexpr int kTcBSlotsMax = kTcBRingBytes / kTcBSlotBytes;   // 6
@@ -142,7 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
     const int kt_end = min(kt_total, kt_begin + p.ktiles_per_cta);
     const int nkt = kt_end - kt_begin;
     constexpr int planes = Q + (BIAS ? 1 : 0);            // q_bias rides as one more plane
-    const int nst = nkt * planes;                         // pipeline stages: (k tile, plane) pairs
+    const int npairs = (nkt + 1) / 2;                     // a stage = (pair of 64-k sub-tiles, plane)
+    const int nst = npairs * planes;
     const size_t rowN = (size_t)N;
     constexpr uint32_t b_slot_bytes = kTcBSlotBytes;
     constexpr int nb_slots = kTcBSlotsMax;
@@ -212,52 +214,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
 #pragma unroll
         for (int c = 0; c < 4; c++) chunk_off[c] = (uint32_t)(((c0 + c) ^ (row & 7)) * 16);
         int cs = 0, cround = 0;                            // shared-memory stage and ring round of the next stage
-        auto expand_tile = [&](const uint32_t (&w)[P], const uint32_t (&a)[P]) {
+        // two weights per register: element t (low half) and t + 16 (high half) of the packed word;
+        // bit set -> +alpha, bit clear -> -alpha (sign bit flipped where the bit is 0); q_bias plane: no sign
+        auto expand_word = [&](uint32_t w, uint32_t a, bool is_bias, unsigned char* dst) {
+            uint32_t nat[16];
+            if (!is_bias) {
+                uint32_t h[16];
+#pragma unroll
+                for (int t = 0; t < 16; t++) {
+                    const uint32_t sh = (t == 15) ? w : (w << (15 - t));
+                    h[t] = a ^ (~sh & 0x80008000u);
+                }
+                // natural k order: (0,1), (2,3), ... then (16,17), ...
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    nat[j] = prmt_b32(h[2 * j], h[2 * j + 1], 0x5410u);
+                    nat[j + 8] = prmt_b32(h[2 * j], h[2 * j + 1], 0x7632u);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) nat[j] = a;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                *reinterpret_cast<uint4*>(dst + chunk_off[c]) = make_uint4(nat[4 * c], nat[4 * c + 1], nat[4 * c + 2], nat[4 * c + 3]);
+        };
+        auto expand_pair = [&](const uint32_t (&w0)[P], const uint32_t (&a0)[P], const uint32_t (&w1)[P], const uint32_t (&a1)[P]) {
 #pragma unroll
             for (int b = 0; b < P; b++) {
                 if (timed_out) break;
                 if (cround > 0) {
                     if (!mbar_wait_bounded(bar_empty + 8 * cs, (cround - 1) & 1)) { timed_out = true; break; }
                 }
-                // two weights per register: element t (low half) and t + 16 (high half) of the word;
-                // bit set -> +alpha, bit clear -> -alpha (sign bit flipped where the bit is 0)
-                uint32_t nat[16];
-                if (b < Q) {
-                    uint32_t h[16];
-#pragma unroll
-                    for (int t = 0; t < 16; t++) {
-                        const uint32_t sh = (t == 15) ? w[b] : (w[b] << (15 - t));
-                        h[t] = a[b] ^ (~sh & 0x80008000u);
-                    }
-                    // natural k order: (0,1), (2,3), ... then (16,17), ...
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        nat[j] = prmt_b32(h[2 * j], h[2 * j + 1], 0x5410u);
-                        nat[j + 8] = prmt_b32(h[2 * j], h[2 * j + 1], 0x7632u);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) nat[j] = a[b];   // q_bias plane: the same value, no sign
-                }
                 unsigned char* dst = smem + cs * kTcAStageBytes + row_off;
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-                    *reinterpret_cast<uint4*>(dst + chunk_off[c]) = make_uint4(nat[4 * c], nat[4 * c + 1], nat[4 * c + 2], nat[4 * c + 3]);
+                expand_word(w0[b], a0[b], b >= Q, dst);
+                expand_word(w1[b], a1[b], b >= Q, dst + kTcASubBytes);
                 fence_proxy_async_smem();                  // make the generic-proxy stores visible to the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_afull + 8 * cs);
                 if (++cs == kTcStages) { cs = 0; cround++; }
             }
         };
-        uint32_t wA[P], aA[P], wB[P], aB[P];
-        load_tile(wA, aA);
-        load_tile(wB, aB);
-        for (int j = 0; j < nkt && !timed_out; j += 2) {
-            expand_tile(wA, aA);
-            load_tile(wA, aA);
-            if (j + 1 < nkt && !timed_out) {
-                expand_tile(wB, aB);
-                load_tile(wB, aB);
+        constexpr int NP = (P <= 5) ? 2 : 1;               // pairs of sub-tiles held in registers ahead of their use
+        uint32_t wq[2 * NP][P], aq[2 * NP][P];
+#pragma unroll
+        for (int u = 0; u < 2 * NP; u++) load_tile(wq[u], aq[u]);
+        for (int j = 0; j < npairs && !timed_out; j += NP) {
+#pragma unroll
+            for (int u = 0; u < NP; u++) {
+                if (j + u < npairs && !timed_out) {
+                    expand_pair(wq[2 * u], aq[2 * u], wq[2 * u + 1], aq[2 * u + 1]);
+                    load_tile(wq[2 * u], aq[2 * u]);
+                    load_tile(wq[2 * u + 1], aq[2 * u + 1]);
+                }
             }
         }
     } else if (warp == kTcExpWarps) {
@@ -265,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
         if (lane == 0) {
             tma_prefetch_descriptor(&tmX);
             int slot = 0, round = 0;
-            for (int j = 0; j < nkt; j++) {
+            for (int j = 0; j < 2 * npairs; j++) {         // sub-tiles, an even number (a trailing one is all padding)
                 if (round > 0) {
                     if (!mbar_wait_bounded(bar_bempty + 8 * slot, (round - 1) & 1)) { timed_out = true; break; }
                 }
@@ -281,23 +290,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16_f32(kTcTileN);
             int s = 0, sround = 0, bslot = 0, bround = 0;
-            for (int j = 0; j < nkt && !timed_out; j++) {
-                if (!mbar_wait_bounded(bar_bfull + 8 * bslot, bround & 1)) { timed_out = true; break; }
+            const uint64_t dx0 = umma_desc_k_sw128(b_base), dw0 = umma_desc_k_sw128(a_base);
+            for (int j = 0; j < npairs && !timed_out; j++) {
+                // the pair's two activation slots
+                if (!mbar_wait_bounded(bar_bfull + 8 * bslot, bround & 1) ||
+                    !mbar_wait_bounded(bar_bfull + 8 * (bslot + 1), bround & 1)) { timed_out = true; break; }
                 for (int b = 0; b < planes; b++) {
                     if (!mbar_wait_bounded(bar_afull + 8 * s, sround & 1)) { timed_out = true; break; }
                     tc_fence_after_sync();
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; k16++) {
-                        // M-side operand: activations; N-side operand: this plane's +-alpha tile
-                        const uint64_t dx = umma_desc_k_sw128(b_base + bslot * b_slot_bytes + k16 * 32);
-                        const uint64_t dw = umma_desc_k_sw128(a_base + s * kTcAStageBytes + k16 * 32);
-                        umma_f16_ss(tmem_acc, dx, dw, idesc, (j > 0 || b > 0 || k16 > 0) ? 1u : 0u);
+                    for (int half = 0; half < 2; half++) {
+#pragma unroll
+                        for (int k16 = 0; k16 < 4; k16++) {
+                            // M-side operand: activations; N-side operand: this plane's +-alpha tile (descriptor start address in 16-byte units)
+                            const uint64_t dx = dx0 + (uint64_t)(((bslot + half) * b_slot_bytes + k16 * 32) >> 4);
+                            const uint64_t dw = dw0 + (uint64_t)((s * kTcAStageBytes + half * kTcASubBytes + k16 * 32) >> 4);
+                            umma_f16_ss(tmem_acc, dx, dw, idesc, (j > 0 || b > 0 || half > 0 || k16 > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(bar_empty + 8 * s);        // weight stage reusable once these MMAs have read it
                     if (++s == kTcStages) { s = 0; sround++; }
                 }
-                umma_commit(bar_bempty + 8 * bslot);       // activation slot reusable after the last plane of the k tile
-                if (++bslot == nb_slots) { bslot = 0; bround++; }
+                umma_commit(bar_bempty + 8 * bslot);       // activation slots reusable after the last plane of the pair
+                umma_commit(bar_bempty + 8 * (bslot + 1));
+                bslot += 2;
+                if (bslot == nb_slots) { bslot = 0; bround++; }
             }
             umma_commit(bar_acc);                          // accumulator complete
         }
@@ -323,15 +340,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const TcParams p) {
                 }
                 if (mrow < p.m) {
                     const size_t base = (size_t)mrow * rowN + n0 + nc;
+                    if ((N & 7) == 0 && n0 + nc + 16 <= N) {
+                        // 16 consecutive columns of one row: vector reductions / vector stores
+                        if (split) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        if (n0 + nc + j < N) {
-                            const float v = __uint_as_float(r[j]);
-                            if (split) {
-                                atomicAdd(p.partial + base + j, v);
-                            } else {
-                                if (p.y32) p.y32[base + j] = v;
-                                if (p.y16) p.y16[base + j] = __float2half_rn(v);
+                            for (int j = 0; j < 16; j += 4)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + base + j),
+                                             "f"(__uint_as_float(r[j])), "f"(__uint_as_float(r[j + 1])),
+                                             "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3])) : "memory");
+                        } else {
+                            if (p.y32) {
+#pragma unroll
+                                for (int j = 0; j < 16; j += 4)
+                                    *reinterpret_cast<float4*>(p.y32 + base + j) =
+                                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            }
+                            if (p.y16) {
+                                uint32_t hh[8];
+#pragma unroll
+                                for (int j = 0; j < 8; j++) {
+                                    __half2 h2 = __floats2half2_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                    hh[j] = *reinterpret_cast<uint32_t*>(&h2);
+                                }
+                                *reinterpret_cast<uint4*>(p.y16 + base) = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+                                *reinterpret_cast<uint4*>(p.y16 + base + 8) = make_uint4(hh[4], hh[5], hh[6], hh[7]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if (n0 + nc + j < N) {
+                                const float v = __uint_as_float(r[j]);
+                                if (split) {
+                                    atomicAdd(p.partial + base + j, v);
+                                } else {
+                                    if (p.y32) p.y32[base + j] = v;
+                                    if (p.y16) p.y16[base + j] = __float2half_rn(v);
+                                }
                             }
                         }
                     }
