@@ -35,9 +35,10 @@ from lutgemm_b200 import synth  # noqa: E402
 METRIC = "bcq_gemv_effective_bandwidth"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_lut_kernel launch at the bench shape,
-# from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tma_kernel launch at the default bench shape
+# (N = K = 12288, q = 3, g = 128, m = 1), from the ncu capture summarised in
+# profiles/gemv_tma_kernel_12288x12288_q3_g128.md: 63 803 392 + 163 584 bytes.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 63966976
 
 
 def parse():
@@ -462,7 +463,8 @@ def run_ours(a):
         "packed_weight_GBps": a.n * a.k * a.q / 8 / (us_per_gemv * 1e-6) / 1e9,
         "pct_of_8TBps_nominal": 100.0 * achieved / 8000.0,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_kind, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": kernel_name},
+                     "peak_source": peak_kind, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (a.n, a.k, a.q, a.g, a.m, a.bias, a.variant) == (12288, 12288, 3, 128, 1, False, 0) else None,
+                     "kernel": kernel_name},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

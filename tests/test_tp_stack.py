@@ -159,3 +159,38 @@ def test_fused_stack_two_gpus_matches_nccl_stack():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     lines = [l for l in out.stdout.splitlines() if l.startswith("TPRESULT")]
     assert out.returncode == 0 and len(lines) == 2 and all("ok=True" in l for l in lines), out.stdout[-2000:] + out.stderr[-2000:]
+
+
+@pytest.mark.gpu
+def test_peer_wait_runs_out_and_reports_status():
+    """A tensor-parallel input whose flag nobody raises: the kernel's bounded wait gives up, the container's
+    status word reports it (4 = peer time-out), nothing hangs, and the context keeps working."""
+    import ctypes as C
+    torch = pytest.importorskip("torch")
+    import lutgemm_b200 as L
+    from lutgemm_b200 import capi
+    N, K, q, g = 512, 512, 2, 128
+    bW, alpha, _ = synth.bcq_layer(N, K, q, g, seed=3)
+    w = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g)
+    x = torch.from_numpy(synth.activations(1, K, seed=1).view(np.int16)).cuda().view(torch.float16)
+    y = torch.zeros((1, N), dtype=torch.float16, device="cuda")
+    words = torch.zeros(8, dtype=torch.int32, device="cuda")          # [0] = flag that stays 0, [1] = done counter
+    link = capi.TpLink()
+    link.world, link.x_mode, link.out_mode = 1, 1, 0
+    link.flag_in, link.flag_target, link.done_counter = words.data_ptr(), 1, words.data_ptr() + 4
+    lib = capi.lib()
+    rc = lib.lutgemm_matvec_tp(x.data_ptr(), w.handle, C.byref(link), y.data_ptr(), None,
+                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == capi.OK
+    torch.cuda.synchronize()                                          # returns: the wait is bounded
+    st = C.c_int(-1)
+    capi.check(lib.lutgemm_weight_device_status(w.handle, C.byref(st)), "device_status")
+    assert st.value & 4
+    assert int(words[0].item()) == 0 and int(words[1].item()) == 0    # the kernel re-armed its words
+    # the context is intact: an ordinary matvec on a fresh container is still right
+    w2 = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g)
+    L.matmul(y, x, w2, 1)
+    torch.cuda.synchronize()
+    ref = oracle.bcq_matmul_fp32(synth.activations(1, K, seed=1), bW, alpha.astype(np.float16), None, g)
+    assert np.abs(y.float().cpu().numpy() - ref).max() <= 1e-2 * np.abs(ref).max()
+    w.close(); w2.close()
