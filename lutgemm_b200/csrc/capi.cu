@@ -14,8 +14,8 @@
 #include <cuda_runtime.h>
 
 #include "aux_kernels.cuh"
-#include "gemv_lut.cuh"
 #include "gemv_tma.cuh"
+#include "gemv_reg.cuh"
 #include "gemm_tc.cuh"
 
 struct lutgemm_weight {
@@ -209,17 +209,27 @@ int launch_gemv_tma(const lutgemm_weight* w, const lg::Gemv2Params& p, dim3 grid
     return LUTGEMM_OK;
 }
 
-template <int Q>
-int launch_gemv_q(const lg::GemvParams& p, dim3 grid, bool bias, cudaStream_t st) {
+template <int WPG>
+int launch_gemv_reg(const lg::Gemv2Params& p, dim3 grid, bool bias, cudaStream_t st) {
     static bool configured[64][2] = {};   // the attribute is per device
-    auto kern = bias ? lg::gemv_lut_kernel<Q, true> : lg::gemv_lut_kernel<Q, false>;
+    auto kern = bias ? lg::gemv_reg_kernel<WPG, true> : lg::gemv_reg_kernel<WPG, false>;
     int dev = 0;
     LG_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev][bias]) {
-        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kLutBytes));
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kRegSmemBytes));
         if (dev < 64) configured[dev][bias] = true;
     }
-    kern<<<grid, lg::kGemvThreads, lg::kLutBytes, st>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(lg::kRegThreads);
+    cfg.dynamicSmemBytes = (size_t)lg::kRegSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    LG_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;
@@ -252,47 +262,26 @@ int launch_gemv_tma_any(const lutgemm_weight* w, const __half* x, __half* y16, f
 // One matvec row: y (fp16 and/or fp32) = x . W
 int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
     const bool use_tma = (g_variant.load() == 0) && w->tma_ok;
-    const bool fast = use_tma || ((w->N % 4 == 0) && (w->K % 256 == 0));
-    if (!fast) {
-        dim3 grid((w->N + 127) / 128);
-        lg::gemv_generic_kernel<<<grid, 128, 0, st>>>(w->bW, w->alpha, w->q_bias, x, y16, y32, w->N, w->K, w->q, w->g);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        LG_CUDA(cudaGetLastError());
-        return LUTGEMM_OK;
+    if (use_tma) return launch_gemv_tma_any(w, x, y16, y32, nullptr, st);
+    if (w->N % 4 == 0) {
+        // register-fed kernel: any group size that is a multiple of 32
+        lg::Gemv2Params p = {};
+        p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
+        p.partial = w->partial; p.counters = w->counters; p.status = w->status; p.y16 = y16; p.y32 = y32;
+        p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
+        p.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
+        p.n_tile = choose_ntile(w->N, p.nslabs, 1, lg::kStageCols);
+        p.ordered = g_ordered.load();
+        dim3 grid((w->N + p.n_tile - 1) / p.n_tile, p.nslabs);
+        const bool bias = w->q_bias != nullptr;
+        if (w->g % 128 == 0) return launch_gemv_reg<2>(p, grid, bias, st);
+        return launch_gemv_reg<1>(p, grid, bias, st);
     }
-    if (use_tma) {
-        lg::Gemv2Params p2 = {};
-        p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
-        p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
-        p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
-        p2.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
-        p2.a_rows = w->a_rows;
-        p2.ordered = g_ordered.load();
-        p2.n_tile = choose_ntile(w->N, p2.nslabs, 1, lg::kStageCols);
-        dim3 grid2((w->N + p2.n_tile - 1) / p2.n_tile, p2.nslabs);
-        const bool bias2 = w->q_bias != nullptr;
-        if (w->g % 128 == 0) return launch_gemv_tma<2>(w, p2, grid2, bias2, st);
-        return launch_gemv_tma<1>(w, p2, grid2, bias2, st);
-    }
-    lg::GemvParams p;
-    p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
-    p.partial = w->partial; p.counters = w->counters; p.y16 = y16; p.y32 = y32;
-    p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
-    p.nslabs = (w->K + lg::kSlabK - 1) / lg::kSlabK;
-    p.n_tile = choose_ntile(w->N, p.nslabs, 2, lg::kCtaCols);
-    dim3 grid((w->N + p.n_tile - 1) / p.n_tile, p.nslabs);
-    const bool bias = w->q_bias != nullptr;
-    switch (w->q) {
-        case 1: return launch_gemv_q<1>(p, grid, bias, st);
-        case 2: return launch_gemv_q<2>(p, grid, bias, st);
-        case 3: return launch_gemv_q<3>(p, grid, bias, st);
-        case 4: return launch_gemv_q<4>(p, grid, bias, st);
-        case 5: return launch_gemv_q<5>(p, grid, bias, st);
-        case 6: return launch_gemv_q<6>(p, grid, bias, st);
-        case 7: return launch_gemv_q<7>(p, grid, bias, st);
-        case 8: return launch_gemv_q<8>(p, grid, bias, st);
-    }
-    return LUTGEMM_ERR_BITS;
+    dim3 grid((w->N + 127) / 128);
+    lg::gemv_generic_kernel<<<grid, 128, 0, st>>>(w->bW, w->alpha, w->q_bias, x, y16, y32, w->N, w->K, w->q, w->g);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
 }
 
 template <int Q>

@@ -221,6 +221,64 @@ __device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, 
     }
 }
 
+// Split-k finish shared by the matvec kernels: called by every thread of the CTA after its partial sums are
+// out.  The last CTA of the column tile [n_begin, n_end) either adds the slabs in slab order or reads the row
+// of L2-reduced sums and zeroes it again for the next launch; one fp16 rounding either way; then the
+// tensor-parallel output links, if any.
+template <int THREADS>
+__device__ __forceinline__ void splitk_finish(const Gemv2Params& p, int tid, int n_begin, int n_end, int* s_flag) {
+    const size_t rowN = (size_t)p.N;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(p.counters + blockIdx.x, 1u);
+        *s_flag = (prev == (unsigned)p.nslabs - 1u);
+    }
+    __syncthreads();
+    if (!*s_flag) return;
+    __threadfence();
+    for (int c = n_begin + 4 * tid; c < n_end; c += 4 * THREADS) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* src = p.partial + c;
+        int sl = 0;
+        if (!p.ordered) {
+            s = __ldcg(reinterpret_cast<const float4*>(src));
+            __stcg(reinterpret_cast<float4*>(p.partial + c), make_float4(0.f, 0.f, 0.f, 0.f));
+            sl = p.nslabs;
+        }
+        for (; sl + 8 <= p.nslabs; sl += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sl + i) * rowN));
+#pragma unroll
+            for (int i = 0; i < 8; i++) { s.x += v[i].x; s.y += v[i].y; s.z += v[i].z; s.w += v[i].w; }
+        }
+        for (; sl < p.nslabs; sl++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sl * rowN));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        if (p.tp.out_mode == 0) {
+            if (p.y32) *reinterpret_cast<float4*>(p.y32 + c) = s;
+            if (p.y16) *reinterpret_cast<uint2*>(p.y16 + c) = o;
+        } else if (p.tp.out_mode == 1) {
+            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<uint2*>(p.tp.out16[r] + p.tp.out_off + c) = o;   // peer stores
+        } else {
+            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<float4*>(p.tp.out32[r] + c) = s;                  // peer stores
+        }
+    }
+    if (p.tp.out_mode != 0) {
+        // publish this tile to every rank: data first (system-scope fence by every storing thread), then the flag
+        __threadfence_system();
+        __syncthreads();
+        if (tid < p.tp.world) red_release_sys_add(p.tp.flag_out[tid], 1u);
+    }
+    if (tid == 0) p.counters[blockIdx.x] = 0u;   // ready for the next launch on this stream
+}
+
 // WPG: packed words per alpha group among a lane's two words of a stage (2: g % 128 == 0, else 1).
 // BIAS: container has q_bias.  tmW: 3-D map {N, q, K/32} of uint32, box {256, 1, 16};
 // tmA: 3-D map {N, q, G} of fp16, box {256, 1, a_rows}.
@@ -426,57 +484,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
     }
 
-    // Split-k finish by the last CTA of this column tile: either add the slabs in slab order, or read
-    // the row of L2-reduced sums and zero it again for the next launch; one fp16 rounding either way.
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned prev = atomicAdd(p.counters + blockIdx.x, 1u);
-        *s_flag = (prev == (unsigned)p.nslabs - 1u);
-    }
-    __syncthreads();
-    if (!*s_flag) return;
-    __threadfence();
-    for (int c = n_begin + 4 * tid; c < n_end; c += 4 * kGemv2Threads) {
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float* src = p.partial + c;
-        int sl = 0;
-        if (!p.ordered) {
-            s = __ldcg(reinterpret_cast<const float4*>(src));
-            __stcg(reinterpret_cast<float4*>(p.partial + c), make_float4(0.f, 0.f, 0.f, 0.f));
-            sl = p.nslabs;
-        }
-        for (; sl + 8 <= p.nslabs; sl += 8) {
-            float4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sl + i) * rowN));
-#pragma unroll
-            for (int i = 0; i < 8; i++) { s.x += v[i].x; s.y += v[i].y; s.z += v[i].z; s.w += v[i].w; }
-        }
-        for (; sl < p.nslabs; sl++) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sl * rowN));
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-        }
-        __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
-        uint2 o;
-        o.x = *reinterpret_cast<uint32_t*>(&lo);
-        o.y = *reinterpret_cast<uint32_t*>(&hi);
-        if (p.tp.out_mode == 0) {
-            if (p.y32) *reinterpret_cast<float4*>(p.y32 + c) = s;
-            if (p.y16) *reinterpret_cast<uint2*>(p.y16 + c) = o;
-        } else if (p.tp.out_mode == 1) {
-            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<uint2*>(p.tp.out16[r] + p.tp.out_off + c) = o;   // peer stores
-        } else {
-            for (int r = 0; r < p.tp.world; r++) *reinterpret_cast<float4*>(p.tp.out32[r] + c) = s;                  // peer stores
-        }
-    }
-    if (p.tp.out_mode != 0) {
-        // publish this tile to every rank: data first (system-scope fence by every storing thread), then the flag
-        __threadfence_system();
-        __syncthreads();
-        if (tid < p.tp.world) red_release_sys_add(p.tp.flag_out[tid], 1u);
-    }
-    if (tid == 0) p.counters[blockIdx.x] = 0u;   // ready for the next launch on this stream
+    splitk_finish<kGemv2Threads>(p, tid, n_begin, n_end, s_flag);
 }
 
 // Last consumer of a tensor-parallel chain: waits for the ranks' fp32 rows, adds them in rank order and writes
