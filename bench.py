@@ -46,7 +46,10 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="reference: the reference's CPU path; reference-gpu (helper leg): the reference's own CUDA kernels, "
+                         "compiled for sm_100a into oracle/_ref/libref_gpu.so, on the same matvec")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference-CUDA-kernel leg of the default run")
     ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack"],
                     help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
@@ -191,6 +194,53 @@ def run_reference(a):
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(a):
+    """The reference's CUDA path (lutGEMM::matmul -> cudaMemset + _nqmv / _nqmv_bias, lutGEMM/src/kernels.cu:64-71)
+    recompiled for sm_100a, timed on the same matvec with the same rotation of weight sets.  Prints one small JSON line."""
+    import ctypes as C
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so")
+    if not os.path.exists(so) or a.m != 1:
+        print(json.dumps({"reference_gpu": None, "why": "oracle/_ref/libref_gpu.so not built" if a.m == 1 else "m > 1"}))
+        return
+    R = C.CDLL(so)
+    R.ref_gpu_create.restype = C.c_void_p
+    R.ref_gpu_create.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+    R.ref_gpu_matmul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+    torch.cuda.set_device(0)
+    rot = max(1, a.rot)
+    keep, ws = [], []
+    for i in range(rot):
+        bW, alpha, qb = synth.bcq_layer(a.n, a.k, a.q, a.g, seed=synth.seed_for("bench", a.n, a.k, a.q, i), with_bias=a.bias)
+        keep.append((bW, alpha, qb))
+        ws.append(R.ref_gpu_create(bW.ctypes.data, alpha.ctypes.data, None if qb is None else qb.ctypes.data, a.k, a.n, a.q, a.k // a.g))
+    x_host = synth.activations(1, a.k, seed=123)
+    x = torch.from_numpy(x_host.view(np.int16)).cuda().view(torch.float16)
+    y = torch.empty((1, a.n), dtype=torch.float16, device="cuda")
+    for _ in range(3):
+        for w in ws:
+            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, 1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(1, min(a.steps, 20))
+    e0.record()
+    for _ in range(steps):
+        for w in ws:
+            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, 1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * rot)
+    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)
+    # accuracy of the reference kernel on the last weight set, against the fp32 host evaluation
+    from oracle import oracle
+    bW, alpha, qb = keep[-1]
+    ref = oracle.bcq_matmul_fp32(x_host, bW, alpha.astype(np.float16), None if qb is None else qb.astype(np.float16), a.g)
+    got = y.float().cpu().numpy()
+    print(json.dumps({"reference_gpu": {"us_per_matvec": us, "value": B / (us * 1e-6) / 1e9, "unit": UNIT,
+                                        "kernel": "_nqmv_bias<32>" if a.bias else "_nqmv<64>", "launches_per_matvec": 2,
+                                        "mae_vs_fp32_host": float(np.abs(got - ref).mean())}}), flush=True)
 
 
 def shutdown_process_group(dist_mod):
@@ -350,7 +400,7 @@ def run_ours(a):
     lib.lutgemm_set_gemv_variant(a.variant)
     lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
     lib.lutgemm_set_ordered_reduction(1 if a.ordered else 0)
-    kernel_name = ("gemv_tma_kernel" if a.variant == 0 else "gemv_reg_kernel") if a.m == 1 else "gemm_tc_kernel"
+    kernel_name = ("gemv_tma_kernel" if a.variant == 0 else "gemv_reg_kernel") if a.m < 5 else "gemm_tc_kernel"
 
     B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, a.m, a.bias)
     rot = max(1, a.rot)
@@ -473,6 +523,16 @@ def run_ours(a):
     if a.m > 1:
         line["tensor_flops_per_matmul"] = 2.0 * a.m * a.n * a.k * (a.q + (1 if a.bias else 0))
         line["tensor_TFLOPs"] = line["tensor_flops_per_matmul"] / (us_per_gemv * 1e-6) / 1e12
+    if world == 1 and a.m == 1 and not a.no_reference_gpu and not a.no_cpu_baseline:
+        # the reference's own CUDA kernels on the same matvec, in a child process (a fault there cannot take this run down)
+        try:
+            child = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--n", str(a.n), "--k", str(a.k),
+                                    "--q", str(a.q), "--g", str(a.g), "--rot", str(rot), "--steps", "10"] + (["--bias"] if a.bias else []),
+                                   capture_output=True, text=True, timeout=180)
+            rows = [l for l in child.stdout.splitlines() if l.startswith("{")]
+            line["reference_gpu"] = json.loads(rows[-1])["reference_gpu"] if rows else None
+        except Exception:
+            line["reference_gpu"] = None
     if world == 1 and not a.no_cpu_baseline and a.m == 1:
         threads = 1
         dt, kind, y_cpu = cpu_reference_gemv(a, threads)
@@ -494,6 +554,8 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         world_size = int(os.environ.get("WORLD_SIZE", "1"))
         workload = args.workload if args.workload != "auto" else ("gemv" if world_size == 1 else "stack")

@@ -223,9 +223,10 @@ int lutgemm_set_gemv_variant(int variant);
  * while no matvec is in flight.  (The reference's half2 atomicAdd accumulation,
  * lutGEMM/src/cuda/kernels/mv_fp16.hpp:95, has no ordered mode.) */
 int lutgemm_set_ordered_reduction(int enabled);
-/* 1 (default): m >= 2 runs the tensor-core (tcgen05) kernel, 128 rows per launch; 0: one LUT matvec
- * per row.  Both compute the same function. */
-int lutgemm_set_batched_path(int enabled);
+/* 1 (default): m >= 5 runs the tensor-core (tcgen05) kernel, 128 rows per launch, smaller batches one LUT
+ * matvec per row; 0: always one LUT matvec per row; 2: tensor-core kernel from m = 2.  All compute the same
+ * function. */
+int lutgemm_set_batched_path(int mode);
 /* Tuning knob: 1 (default) launches the TMA-fed matvec with programmatic stream serialization, so
  * that its weight stream starts while the previous kernel of the stream drains; 0 = plain launches. */
 int lutgemm_set_dependent_launch(int enabled);
