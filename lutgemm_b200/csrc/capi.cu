@@ -34,6 +34,10 @@ struct lutgemm_weight {
     CUtensorMap tmW, tmA;
     bool tma_ok = false;
     int a_rows = 1;            // alpha groups per 512-k slab
+    // TMA descriptors of the batched (tensor-core) path: planes box {256, q, 4}, alpha box {256, q, groups per 128 k},
+    // q_bias box {256, groups per 128 k} (valid when tc_ok)
+    CUtensorMap tmWtc, tmAtc, tmQtc;
+    bool tc_ok = false;
     // fp32 split-k workspace of the batched (tensor-core) path, [tc_rows][N], grown on demand, kept zeroed
     float* tc_partial = nullptr;
     int tc_rows = 0;
@@ -98,8 +102,45 @@ EncodeTiledFn encode_tiled_fn() {
 // Descriptors for the TMA-fed matvec: planes as {N, q, K/32} uint32 with box {256, 1, 16}; alpha as
 // {N, q, G} fp16 with box {256, 1, groups per 512-k slab}.  Leaves tma_ok false when the shape does
 // not qualify (N % 8, group size neither dividing nor a multiple of 512) or the driver refuses.
+void make_tc_tensor_maps(lutgemm_weight* w, EncodeTiledFn enc) {
+    w->tc_ok = false;
+    const int g = w->g;
+    if (w->N % 8 != 0 || !((lg::kTcStepK % g == 0) || (g % lg::kTcStepK == 0))) return;
+    const int a_rows = g >= lg::kTcStepK ? 1 : lg::kTcStepK / g;
+    const cuuint64_t N = (cuuint64_t)w->N, q = (cuuint64_t)w->q;
+    cuuint32_t es[3] = {1, 1, 1};
+    {
+        cuuint64_t dims[3] = {N, q, (cuuint64_t)(w->K / 32)};
+        cuuint64_t strides[2] = {N * 4, q * N * 4};
+        cuuint32_t box[3] = {(cuuint32_t)lg::kTcTileN, (cuuint32_t)w->q, (cuuint32_t)lg::kTcStepWords};
+        if (enc(&w->tmWtc, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, w->bW, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return;
+    }
+    {
+        cuuint64_t dims[3] = {N, q, (cuuint64_t)w->G};
+        cuuint64_t strides[2] = {N * 2, q * N * 2};
+        cuuint32_t box[3] = {(cuuint32_t)lg::kTcTileN, (cuuint32_t)w->q, (cuuint32_t)a_rows};
+        if (enc(&w->tmAtc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, w->alpha, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return;
+    }
+    w->tmQtc = w->tmAtc;                                   // placeholder when there is no q_bias (never read)
+    if (w->q_bias) {
+        cuuint64_t dims[2] = {N, (cuuint64_t)w->G};
+        cuuint64_t strides[1] = {N * 2};
+        cuuint32_t box[2] = {(cuuint32_t)lg::kTcTileN, (cuuint32_t)a_rows};
+        if (enc(&w->tmQtc, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->q_bias, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return;
+    }
+    w->tc_ok = true;
+}
+
 void make_tensor_maps(lutgemm_weight* w) {
     w->tma_ok = false;
+    w->tc_ok = false;
+    if (EncodeTiledFn e = encode_tiled_fn()) make_tc_tensor_maps(w, e);
     const int g = w->g;
     if (w->N % 8 != 0 || !((lg::kSlab2 % g == 0) || (g % lg::kSlab2 == 0))) return;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -286,33 +327,35 @@ int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, 
 }
 
 template <int Q>
-int launch_gemm_tc_q(const CUtensorMap& tmX, const lg::TcParams& p, dim3 grid, cudaStream_t st) {
+int launch_gemm_tc_q(const lutgemm_weight* w, const CUtensorMap& tmX, const lg::TcParams& p, dim3 grid, cudaStream_t st) {
     static bool configured[64][2] = {};   // the attribute is per device
-    const bool bias = p.q_bias != nullptr;
+    const bool bias = w->q_bias != nullptr;
     auto kern = bias ? lg::gemm_tc_kernel<Q, true> : lg::gemm_tc_kernel<Q, false>;
     int dev = 0;
     LG_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev][bias]) {
-        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemBytes));
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemTotal));
         if (dev < 64) configured[dev][bias] = true;
     }
-    kern<<<grid, lg::kTcThreads, lg::kTcSmemBytes, st>>>(tmX, p);
+    kern<<<grid, lg::kTcThreads, p.L.smem_bytes, st>>>(tmX, w->tmWtc, w->tmAtc, w->tmQtc, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;
 }
 
-// Batched rows [0, m), m in 2..128, through the tensor-core kernel.
+// Batched rows [0, m), m in 2..128, through the tensor-core kernel (container must have tc_ok).
 int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
     EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return LUTGEMM_ERR_CUDA;
-    lg::TcParams p;
+    if (!enc || !w->tc_ok) return LUTGEMM_ERR_CUDA;
+    lg::TcParams p = {};
     p.m = m;
+    p.L = lg::tc_layout(w->q, w->q_bias != nullptr, w->g, m);
+    if (p.L.w_slots < 1 || p.L.x_slots < 1) return LUTGEMM_ERR_TOO_LARGE;
     CUtensorMap tmX;
     {
         cuuint64_t dims[2] = {(cuuint64_t)w->K, (cuuint64_t)m};
         cuuint64_t strides[1] = {(cuuint64_t)w->K * 2};
-        cuuint32_t box[2] = {64, (cuuint32_t)lg::kTcTileM};
+        cuuint32_t box[2] = {64, (cuuint32_t)p.L.m_pad};
         cuuint32_t es[2] = {1, 1};
         if (enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, es,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -320,19 +363,18 @@ int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, in
             return LUTGEMM_ERR_CUDA;
     }
     const int tiles = (w->N + lg::kTcTileN - 1) / lg::kTcTileN;
-    const int kt_total = (w->K + lg::kTcTileK - 1) / lg::kTcTileK;
+    const int steps_total = (w->K + lg::kTcStepK - 1) / lg::kTcStepK;
     // split-k factor: fill whole waves of one CTA per SM; among equally full choices take the smallest
     const int sms = sm_count();
     int splitk = 1;
     double best = 0.0;
-    for (int c = 1; c <= 8 && c <= kt_total; c++) {
+    for (int c = 1; c <= 8 && c <= steps_total; c++) {
         const int ctas = tiles * c;
         const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
         if (eff > best + 0.02) { best = eff; splitk = c; }
     }
-    p.ktiles_per_cta = (kt_total + splitk - 1) / splitk;
-    p.ktiles_per_cta += p.ktiles_per_cta & 1;            // a pipeline stage holds a pair of 64-k sub-tiles
-    splitk = (kt_total + p.ktiles_per_cta - 1) / p.ktiles_per_cta;
+    p.steps_per_cta = (steps_total + splitk - 1) / splitk;
+    splitk = (steps_total + p.steps_per_cta - 1) / p.steps_per_cta;
     if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
     if (splitk > 1 && w->tc_rows < m) {
         // grow the zeroed fp32 workspace (synchronises; happens once per container and batch size class)
@@ -344,20 +386,19 @@ int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, in
         LG_CUDA(cudaMemset(w->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
         w->tc_rows = rows;
     }
-    p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias;
     p.partial = w->tc_partial; p.counters = w->counters; p.status = w->status;
     p.y16 = y16; p.y32 = y32;
-    p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
+    p.N = w->N; p.K = w->K; p.g = w->g;
     dim3 grid(tiles, splitk);
     switch (w->q) {
-        case 1: return launch_gemm_tc_q<1>(tmX, p, grid, st);
-        case 2: return launch_gemm_tc_q<2>(tmX, p, grid, st);
-        case 3: return launch_gemm_tc_q<3>(tmX, p, grid, st);
-        case 4: return launch_gemm_tc_q<4>(tmX, p, grid, st);
-        case 5: return launch_gemm_tc_q<5>(tmX, p, grid, st);
-        case 6: return launch_gemm_tc_q<6>(tmX, p, grid, st);
-        case 7: return launch_gemm_tc_q<7>(tmX, p, grid, st);
-        case 8: return launch_gemm_tc_q<8>(tmX, p, grid, st);
+        case 1: return launch_gemm_tc_q<1>(w, tmX, p, grid, st);
+        case 2: return launch_gemm_tc_q<2>(w, tmX, p, grid, st);
+        case 3: return launch_gemm_tc_q<3>(w, tmX, p, grid, st);
+        case 4: return launch_gemm_tc_q<4>(w, tmX, p, grid, st);
+        case 5: return launch_gemm_tc_q<5>(w, tmX, p, grid, st);
+        case 6: return launch_gemm_tc_q<6>(w, tmX, p, grid, st);
+        case 7: return launch_gemm_tc_q<7>(w, tmX, p, grid, st);
+        case 8: return launch_gemm_tc_q<8>(w, tmX, p, grid, st);
     }
     return LUTGEMM_ERR_BITS;
 }
@@ -397,7 +438,7 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     // Up to four rows one LUT matvec per row is cheaper than the tensor-core kernel, whose cost is nearly
     // independent of m (measured crossover at 8192^2, q = 2: m x 10.2 us against 46 us).
     const int batched_mode = g_batched.load();
-    if (m == 1 || batched_mode == 0 || (batched_mode == 1 && m < kBatchedFromRows)) {
+    if (m == 1 || batched_mode == 0 || (batched_mode == 1 && m < kBatchedFromRows) || !w->tc_ok) {
         for (int r = 0; r < m; r++) {
             int rc = gemv_row(w, x + (size_t)r * w->K, y16 ? y16 + (size_t)r * w->N : nullptr,
                               y32 ? y32 + (size_t)r * w->N : nullptr, st);

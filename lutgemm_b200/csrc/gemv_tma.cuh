@@ -347,22 +347,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int rr = lane >> 3;                // G: which 128-k run of the slab
         const int cb = warp & 7, h = warp >> 3;
         const int jp = (c8 & 1) ^ h;             // this lane's words in the slab: kw = 4 rr + jp + 2 u, u = 0, 1
-        pdl_wait_prior_grids();                  // the activations may come from the previous kernel
-        if (p.tp.x_mode != 0) {
-            // ... or from the other GPUs: wait for their pushes (bounded), then let the last CTA re-arm the flag
-            if (tid == 0) {
-                if (!wait_flag_bounded(p.tp.flag_in, p.tp.flag_target)) atomicExch(p.status, kStatusPeerTimeout);
-                const unsigned prev = atomicAdd(p.tp.done_counter, 1u);
-                if (prev == gridDim.x * gridDim.y - 1u) {
-                    *reinterpret_cast<volatile unsigned*>(p.tp.flag_in) = 0u;
-                    *reinterpret_cast<volatile unsigned*>(p.tp.done_counter) = 0u;
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
-        }
-        build_lut2(lut, p.x, k0, p.K, tid, p.tp);
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
-
+        // everything that does not depend on the activations comes before the dependency wait
         uint32_t cs = 0, sel[4];
 #pragma unroll
         for (int b = 0; b < 4; b++) cs |= (uint32_t)(32 * rr + 16 * jp + 4 * b) << (8 * b);
@@ -383,6 +368,22 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             arow[gi] = grp[gi] - k0 / p.g;
             grp_ok[gi] = (k0 + 32 * kw_local) < p.K;
         }
+        pdl_wait_prior_grids();                  // the activations may come from the previous kernel
+        if (p.tp.x_mode != 0) {
+            // ... or from the other GPUs: wait for their pushes (bounded), then let the last CTA re-arm the flag
+            if (tid == 0) {
+                if (!wait_flag_bounded(p.tp.flag_in, p.tp.flag_target)) atomicExch(p.status, kStatusPeerTimeout);
+                const unsigned prev = atomicAdd(p.tp.done_counter, 1u);
+                if (prev == gridDim.x * gridDim.y - 1u) {
+                    *reinterpret_cast<volatile unsigned*>(p.tp.flag_in) = 0u;
+                    *reinterpret_cast<volatile unsigned*>(p.tp.done_counter) = 0u;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+        }
+        build_lut2(lut, p.x, k0, p.K, tid, p.tp);
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+
         float xsum[NG];
         if (BIAS) {
             // sum of the activations under each group of words: entries idx = 255 (all signs +)
