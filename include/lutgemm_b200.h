@@ -223,7 +223,7 @@ int lutgemm_set_gemv_variant(int variant);
  * while no matvec is in flight.  (The reference's half2 atomicAdd accumulation,
  * lutGEMM/src/cuda/kernels/mv_fp16.hpp:95, has no ordered mode.) */
 int lutgemm_set_ordered_reduction(int enabled);
-/* 1 (default): m >= 5 runs the tensor-core (tcgen05) kernel, 128 rows per launch, smaller batches one LUT
+/* 1 (default): m >= 4 runs the tensor-core (tcgen05) kernel, 128 rows per launch, smaller batches one LUT
  * matvec per row; 0: always one LUT matvec per row; 2: tensor-core kernel from m = 2.  All compute the same
  * function. */
 int lutgemm_set_batched_path(int mode);

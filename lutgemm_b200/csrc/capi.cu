@@ -59,7 +59,7 @@ std::atomic<int> g_batched{1};   // 0: one matvec per row; 1: tensor-core kernel
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
-constexpr int kBatchedFromRows = 5;      // m >= 5 goes to the tensor-core kernel
+constexpr int kBatchedFromRows = 4;      // m >= 4 goes to the tensor-core kernel
 
 #define LG_CUDA(call)                                  \
     do {                                               \
@@ -435,8 +435,9 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     if (((uintptr_t)in & 15) || ((uintptr_t)y16 & 15) || ((uintptr_t)y32 & 15)) return LUTGEMM_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     const __half* x = (const __half*)in;
-    // Up to four rows one LUT matvec per row is cheaper than the tensor-core kernel, whose cost is nearly
-    // independent of m (measured crossover at 8192^2, q = 2: m x 10.2 us against 46 us).
+    // Up to three rows one LUT matvec per row is cheaper than the tensor-core kernel, whose cost is nearly
+    // independent of m up to 64 rows (measured: 8192^2, q = 2: m x 10.2 us against 29 us; 12288^2, q = 3:
+    // m x 17.6 us against 64 us).
     const int batched_mode = g_batched.load();
     if (m == 1 || batched_mode == 0 || (batched_mode == 1 && m < kBatchedFromRows) || !w->tc_ok) {
         for (int r = 0; r < m; r++) {

@@ -173,7 +173,7 @@ def test_batched_tensor_core_path(N, K, q, g, m, bias):
     bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=synth.seed_for("tc", N, K, q, m), with_bias=bias, signed_alpha=True)
     x = synth.activations(m, K, seed=m)
     ref = oracle_y(bW, alpha, qb, g, x)
-    capi.lib().lutgemm_set_batched_path(2)           # tensor-core kernel from m = 2 (the default starts at m = 5)
+    capi.lib().lutgemm_set_batched_path(2)           # tensor-core kernel from m = 2 (the default starts at m = 4)
     try:
         y16 = run_matmul(bW, alpha, qb, g, x)
         y32 = run_matmul(bW, alpha, qb, g, x, f32=True)
