@@ -201,6 +201,21 @@ int lutgemm_uniform_to_bcq_device(const float* d_scale, const float* d_zero, con
 int lutgemm_from_python_layout(const float* alpha_py, const int8_t* binary_py, const float* offset_py,
                                int N, int K, int g, int q, uint32_t* bW, float* alpha, float* q_bias);
 
+/* BCQ quantiser: replaces quantize() of examples/bcq.py:23-98 (greedy_mean_torch :100-128, refine_mean_torch
+ * :130-157, find_B_torch :165-188, batch_cg_torch :190-206) for its default unweighted case (exponent 0,
+ * clipping 1, pruning 0).  w float [N][K] (output rows, groups of `group_size` consecutive input features;
+ * group_size <= 0: one group per row); `rounds` refinements after the greedy start (the reference's default is
+ * 15; ignored for q == 1).  One warp quantises one group, so group_size <= 1024.  Outputs, each optional
+ * (NULL to skip) in the device form: the quantiser's own layout alpha [N][G][q] / binary int8 [N][G][g][q]
+ * in {-1, 0, +1} (0 only where the greedy start met an exactly zero residual), and the container layout of this
+ * library, bW [K/32][q][N] and alpha fp16 [G][q][N] (needs group_size % 32 == 0; a zero code packs as -1),
+ * ready for lutgemm_weight_create_device.  The host form copies w in and the quantiser's layout out. */
+int lutgemm_bcq_quantize_device(const float* d_w, int N, int K, int q, int group_size, int rounds,
+                                float* d_alpha_py, signed char* d_binary_py, uint32_t* d_bW, void* d_alpha_fp16,
+                                void* stream);
+int lutgemm_bcq_quantize(const float* w, int N, int K, int q, int group_size, int rounds,
+                         float* alpha_py, signed char* binary_py);
+
 /* The Python examples' uint8 interchange format (Packer.pack / Packer.unpack,
  * examples/utils.py:162-181): L values of +-1 <-> L/8 bytes, byte j = sum_i 2^i * [flat[i*L/8 + j] > 0]. */
 int lutgemm_packer_pack(const int8_t* flat_pm1, size_t L, uint8_t* packed);

@@ -220,3 +220,33 @@ def packer_unpack(packed, L):
     out = np.empty(L, np.int8)
     capi.check(capi.lib().lutgemm_packer_unpack(_ptr(packed), L, _ptr(out)), "packer_unpack")
     return out
+
+
+def bcq_quantize(w, qbits, rounds=15, group_size=-1):
+    """The reference's quantize(w, qbits, rounds, group_size) (examples/bcq.py:23-98, unweighted defaults) on the GPU.
+
+    w float32 [N, K] (numpy).  Returns (w_hat [N, K], binary int8 [N, G, g, qbits], alpha float32 [N, G, qbits]) in the
+    quantiser's own layout; from_python_layout() turns (alpha, binary) into the container's.
+    """
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    N, K = w.shape
+    g = group_size if group_size > 0 else K
+    alpha = np.empty((N, K // g, qbits), np.float32)
+    binary = np.empty((N, K // g, g, qbits), np.int8)
+    capi.check(capi.lib().lutgemm_bcq_quantize(_ptr(w), N, K, qbits, group_size, rounds, _ptr(alpha), _ptr(binary)),
+               "bcq_quantize")
+    w_hat = np.einsum("ngkq,ngq->ngk", binary.astype(np.float32), alpha).reshape(N, K)
+    return w_hat, binary, alpha
+
+
+def bcq_quantize_device(d_w, qbits, rounds=15, group_size=-1, stream=None):
+    """Same, torch tensors on the device, straight into the container layout: returns (bW int32 [K/32, q, N],
+    alpha fp16 [G, q, N]) for nQWeight_fp16.from_device; group_size must be a multiple of 32."""
+    import torch
+    N, K = d_w.shape
+    g = group_size if group_size > 0 else K
+    bW = torch.empty((K // 32, qbits, N), dtype=torch.int32, device=d_w.device)
+    alpha = torch.empty((K // g, qbits, N), dtype=torch.float16, device=d_w.device)
+    capi.check(capi.lib().lutgemm_bcq_quantize_device(_ptr(d_w), N, K, qbits, group_size, rounds, None, None, _ptr(bW),
+                                                      _ptr(alpha), _stream_ptr(stream)), "bcq_quantize_device")
+    return bW, alpha

@@ -17,6 +17,7 @@
 #include "gemv_tma.cuh"
 #include "gemv_reg.cuh"
 #include "gemm_tc.cuh"
+#include "bcq_quantize.cuh"
 
 struct lutgemm_weight {
     uint32_t* bW = nullptr;
@@ -853,6 +854,58 @@ int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat) {
         for (size_t j = 0; j < cols; j++) dst[j] = ((packed[j] >> i) & 1) ? 1 : -1;
     }
     return LUTGEMM_OK;
+}
+
+int lutgemm_bcq_quantize_device(const float* d_w, int N, int K, int q, int group_size, int rounds,
+                                float* d_alpha_py, signed char* d_binary_py, uint32_t* d_bW, void* d_alpha_fp16,
+                                void* stream) {
+    if (!d_w || (!d_alpha_py && !d_binary_py && !d_bW && !d_alpha_fp16)) return LUTGEMM_ERR_NULL;
+    if (q < 1 || q > lg::kBqMaxQ) return LUTGEMM_ERR_BITS;
+    const int g = group_size > 0 ? group_size : K;
+    if (N < 1 || K < 1 || rounds < 0 || K % g != 0 || g > 1024) return LUTGEMM_ERR_SHAPE;
+    if ((d_bW || d_alpha_fp16) && (g % 32 != 0)) return LUTGEMM_ERR_SHAPE;
+    lg::BqParams p;
+    p.w = d_w; p.N = N; p.K = K; p.g = g; p.q = q; p.rounds = rounds;
+    p.alpha_py = d_alpha_py; p.binary_py = d_binary_py; p.bW = d_bW; p.alpha_k = (__half*)d_alpha_fp16;
+    const long long groups = (long long)N * (K / g);
+    const long long ctas = (groups + lg::kBqWarps - 1) / lg::kBqWarps;
+    if (ctas > 0x7fffffffLL) return LUTGEMM_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (g <= 128) lg::bcq_quantize_kernel<4><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
+    else if (g <= 256) lg::bcq_quantize_kernel<8><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
+    else lg::bcq_quantize_kernel<32><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_bcq_quantize(const float* w, int N, int K, int q, int group_size, int rounds,
+                         float* alpha_py, signed char* binary_py) {
+    if (!w || !alpha_py || !binary_py) return LUTGEMM_ERR_NULL;
+    if (N < 1 || K < 1) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > lg::kBqMaxQ) return LUTGEMM_ERR_BITS;
+    const int g = group_size > 0 ? group_size : K;
+    if (K % g != 0) return LUTGEMM_ERR_SHAPE;
+    const size_t nw = (size_t)N * K, na = (size_t)N * (K / g) * q;
+    float *d_w = nullptr, *d_a = nullptr;
+    signed char* d_b = nullptr;
+    int rc = LUTGEMM_OK;
+    auto fail = [&](cudaError_t e) {
+        g_last_cuda = (int)e;
+        rc = (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) ? LUTGEMM_ERR_NO_DEVICE : LUTGEMM_ERR_CUDA;
+    };
+    cudaError_t e;
+    if ((e = cudaMalloc(&d_w, nw * sizeof(float))) != cudaSuccess) fail(e);
+    if (rc == LUTGEMM_OK && (e = cudaMalloc(&d_a, na * sizeof(float))) != cudaSuccess) fail(e);
+    if (rc == LUTGEMM_OK && (e = cudaMalloc(&d_b, nw * q)) != cudaSuccess) fail(e);
+    if (rc == LUTGEMM_OK && (e = cudaMemcpy(d_w, w, nw * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) fail(e);
+    if (rc == LUTGEMM_OK) rc = lutgemm_bcq_quantize_device(d_w, N, K, q, group_size, rounds, d_a, d_b, nullptr, nullptr, nullptr);
+    if (rc == LUTGEMM_OK && (e = cudaMemcpy(alpha_py, d_a, na * sizeof(float), cudaMemcpyDeviceToHost)) != cudaSuccess) fail(e);
+    if (rc == LUTGEMM_OK && (e = cudaMemcpy(binary_py, d_b, nw * q, cudaMemcpyDeviceToHost)) != cudaSuccess) fail(e);
+    if (d_w) cudaFree(d_w);
+    if (d_a) cudaFree(d_a);
+    if (d_b) cudaFree(d_b);
+    return rc;
 }
 
 const char* lutgemm_status_string(int s) {
