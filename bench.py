@@ -50,8 +50,11 @@ def parse():
                     help="reference: the reference's CPU path; reference-gpu (helper leg): the reference's own CUDA kernels, "
                          "compiled for sm_100a into oracle/_ref/libref_gpu.so, on the same matvec")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference-CUDA-kernel leg of the default run")
-    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack"],
-                    help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more")
+    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack", "quantize", "gptq"],
+                    help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more; "
+                         "quantize: the BCQ quantiser (greedy + --rounds refinements) on an [n, k] fp32 layer, a side line; "
+                         "gptq: the 3-bit uniform comparison matvec (matmul_gptq), with the reference's two kernels beside it")
+    ap.add_argument("--rounds", type=int, default=15, help="quantize workload: refinement rounds")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
                     help="stack workload: exchange steps fused into the matvec kernels (peer pushes) or NCCL collectives")
     ap.add_argument("--layers", type=int, default=96, help="decoder layers of the stack workload")
@@ -379,6 +382,138 @@ def run_stack(a):
     shutdown_process_group(dist if world > 1 else None)
 
 
+def run_quantize(a):
+    """Side line: the device BCQ quantiser on one synthetic fp32 layer [n, k] straight into the container layout,
+    against the numpy restatement of the reference's torch code on a few rows (host cores)."""
+    import torch
+    import lutgemm_b200 as L
+    from lutgemm_b200 import capi
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    w = torch.randn((a.n, a.k), device="cuda", generator=gen) * 0.02
+    lib = capi.lib()
+    n0 = lib.lutgemm_kernel_launch_count()
+    for _ in range(max(a.warmup, 3)):
+        L.bcq_quantize_device(w, a.q, a.rounds, a.g)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        L.bcq_quantize_device(w, a.q, a.rounds, a.g)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / a.steps
+    weights = a.n * a.k
+    # bytes that have to move: fp32 weights in, packed planes + fp16 scales out
+    alg_bytes = 4 * weights + weights * a.q // 8 + 2 * (a.k // a.g) * a.q * a.n
+    line = {"metric": "bcq_quantize_throughput", "value": weights / ms / 1e3, "unit": "Mweights/s", "n_gpus": 1,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"bcq_quantize n={a.n} k={a.k} q={a.q} g={a.g} rounds={a.rounds}",
+                       "l2": f"input {4 * weights / 1e6:.0f} MB per step" + (" (larger than L2)" if 4 * weights > 126e6 else " (fits L2: compute-bound kernel)")},
+            "roofline": {"bound": "hbm", "achieved": alg_bytes / ms / 1e6, "peak": measured_peak()[0], "unit": "GB/s",
+                         "frac": alg_bytes / ms / 1e6 / measured_peak()[0], "peak_source": measured_peak()[1], "traffic": None,
+                         "kernel": "bcq_quantize_kernel", "note": "arithmetic-bound (q x q solves and 2^q-level search per group), far below the HBM bound"},
+            "gpu_launches": int(lib.lutgemm_kernel_launch_count() - n0) - max(a.warmup, 3), "clocks": clocks}
+    if not a.no_cpu_baseline:
+        from oracle import bcq_quantizer as bq
+        rows = max(1, min(a.n, (1 << 19) // a.k))
+        wh = w[:rows].cpu().numpy()
+        t0 = time.perf_counter()
+        bq.quantize(wh, a.q, a.rounds, a.g)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": rows * a.k / dt / 1e6, "unit": "Mweights/s", "cores": 1, "kind": "port",
+                                "sample": f"{rows} of {a.n} rows, numpy restatement of examples/bcq.py, {dt:.1f} s"}
+    print(json.dumps(line))
+
+
+def run_gptq(a):
+    """Side line: the 3-bit uniform (GPTQ-format) matvec of the reference's header, ours and (when oracle/_ref holds them)
+    the reference's own two kernels, on the same B200; --rot weight sets cycled so that nothing is served from L2."""
+    import ctypes as C
+    import torch
+    import lutgemm_b200 as L
+    from lutgemm_b200 import capi
+    torch.cuda.set_device(0)
+    N, K, rot = a.n, a.k, a.rot
+    kp = K * 3 // 32
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    mats = [torch.randint(-2**31, 2**31 - 1, (kp, N), dtype=torch.int32, device="cuda", generator=gen) for _ in range(rot)]
+    scale = (torch.randn(N, device="cuda", generator=gen).abs() * 0.01).half()
+    zero = (scale.float() * 3.5).half()
+    x = torch.randn((1, K), device="cuda", generator=gen).half()
+    y = torch.empty((1, N), dtype=torch.float16, device="cuda")
+    alg_bytes = kp * N * 4 + 4 * N + 2 * K + 2 * N
+
+    def timed(fn):
+        for _ in range(max(a.warmup, 3)):
+            for m_ in mats:
+                fn(m_)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            for m_ in mats:
+                fn(m_)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (a.steps * rot)
+
+    lib = capi.lib()
+    n0 = lib.lutgemm_kernel_launch_count()
+    sampler = ClockSampler(0)
+    sampler.start()
+    # one step (rot matvecs) captured into a CUDA graph and replayed: the Python call costs more than the kernel
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for m_ in mats:
+            L.matmul_gptq(1, N, kp, scale, zero, x, m_, y)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for m_ in mats:
+                L.matmul_gptq(1, N, kp, scale, zero, x, m_, y)
+    torch.cuda.synchronize()
+    for _ in range(max(a.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a.steps * rot)
+    clocks = sampler.stop()
+    launches = a.steps * rot
+    peak, src = measured_peak()
+    line = {"metric": "gptq3_gemv_effective_bandwidth", "value": alg_bytes / us / 1e3, "unit": "GB/s", "n_gpus": 1,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": us * rot / 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"gptq3_gemv m=1 n={N} k={K}", "matvecs_per_step": rot,
+                       "l2": f"{rot} weight sets cycled ({rot * kp * N * 4 / 1e6:.0f} MB per step)",
+                       "launch": "cuda graph of one step, replayed (reference kernels: direct calls, they use the legacy stream)"},
+            "us_per_matvec": us,
+            "roofline": {"bound": "hbm", "achieved": alg_bytes / us / 1e3, "peak": peak, "unit": "GB/s",
+                         "frac": alg_bytes / us / 1e3 / peak, "peak_source": src, "traffic": None, "kernel": "gptq3_gemv_kernel"},
+            "gpu_launches": launches, "clocks": clocks}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so")
+    if os.path.exists(ref_path) and N % 256 == 0 and K % 256 == 0:      # the reference kernels check no bounds
+        ref = C.CDLL(ref_path)
+        if hasattr(ref, "ref_gpu_matmul_gptq"):
+            ref.ref_gpu_matmul_gptq.argtypes = [C.c_int] * 3 + [C.c_void_p] * 5 + [C.c_int]
+            y2 = torch.empty_like(y)
+            for faster, name in ((0, "VecQuant3MatMulKernel"), (1, "VecQuant3MatMulKernelFaster")):
+                t = timed(lambda m_: ref.ref_gpu_matmul_gptq(1, N, kp, scale.data_ptr(), zero.data_ptr(), x.data_ptr(),
+                                                             m_.data_ptr(), y2.data_ptr(), faster))
+                line.setdefault("reference_gpu", {})[name] = {"us_per_matvec": t, "value": alg_bytes / t / 1e3, "unit": "GB/s",
+                                                              "launches_per_matvec": 2}
+    print(json.dumps(line))
+
+
 def run_ours(a):
     import torch
     import lutgemm_b200 as L
@@ -561,5 +696,9 @@ if __name__ == "__main__":
         workload = args.workload if args.workload != "auto" else ("gemv" if world_size == 1 else "stack")
         if workload == "stack":
             run_stack(args)
+        elif workload == "quantize":
+            run_quantize(args)
+        elif workload == "gptq":
+            run_gptq(args)
         else:
             run_ours(args)

@@ -201,6 +201,15 @@ int lutgemm_uniform_to_bcq_device(const float* d_scale, const float* d_zero, con
 int lutgemm_from_python_layout(const float* alpha_py, const int8_t* binary_py, const float* offset_py,
                                int N, int K, int g, int q, uint32_t* bW, float* alpha, float* q_bias);
 
+/* The 3-bit uniform (GPTQ-format) comparison rows of the reference's header: replaces lutGEMM::matmul_gptq and
+ * lutGEMM::matmul_gptq_faster (lutGEMM/include/kernels.h:28-33, lutGEMM/src/kernels.cu:40-54; kernels
+ * lutGEMM/src/cuda/kernels/gptq_fp16_bias.hpp, gptq_faster_fp16_bias.hpp), same argument order and meaning:
+ * k_packed = K * 3 / 32 rows of `mat` [k_packed][n] (32 codes of 3 bits in three words along k),
+ * out[r][c] = sum_k (scale[c] * code[k][c] - zero[c]) * in[r][k].  fp32 accumulation, one fp16 rounding, no
+ * memset and no atomics; every one of the m rows is computed (the reference kernels compute row 0 only). */
+int lutgemm_matmul_gptq(int m, int n, int k_packed, const void* scale_fp16, const void* zero_fp16,
+                        const void* in_fp16, const uint32_t* mat, void* out_fp16, void* stream);
+
 /* BCQ quantiser: replaces quantize() of examples/bcq.py:23-98 (greedy_mean_torch :100-128, refine_mean_torch
  * :130-157, find_B_torch :165-188, batch_cg_torch :190-206) for its default unweighted case (exponent 0,
  * clipping 1, pruning 0).  w float [N][K] (output rows, groups of `group_size` consecutive input features;

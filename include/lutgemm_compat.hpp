@@ -11,7 +11,7 @@
 // (cudaMalloc) instead of managed memory, so bWeight / alpha / q_bias must not be dereferenced on the
 // host; q_bias is applied for every batch size, not only for batch 1; every call records a status
 // readable through lutGEMM::last_status() instead of failing silently; the destructor frees each
-// buffer exactly once.  The GPTQ comparison kernels (matmul_gptq*) are not part of this library.
+// buffer exactly once; matmul_gptq* compute all m rows in fp32 (the reference kernels compute row 0 in fp16).
 #ifndef LUTGEMM_COMPAT_HPP
 #define LUTGEMM_COMPAT_HPP
 
@@ -104,6 +104,14 @@ inline void matmul(void* output, nQWeight_fp16& nqW, void* input, int n, int alg
 inline void matmul(void* output, void* input, nQWeight_fp16& nqW, int m, int algo = 0) {
     (void)algo;
     last_status_ref() = lutgemm_matmul(output, input, nqW.handle(), m, nullptr);
+}
+// The 3-bit uniform comparison rows (lutGEMM/include/kernels.h:28-33): k = packed rows K * 3 / 32, scale / bias
+// (the zero term) fp16 [n], A fp16 [m][K], B uint32 [k][n], C fp16 [m][n]; out = sum_k (scale * code - bias) * in.
+inline void matmul_gptq(int m, int n, int k, void* scale, void* bias, void* A, void* B, void* C) {
+    last_status_ref() = lutgemm_matmul_gptq(m, n, k, scale, bias, A, (const uint32_t*)B, C, nullptr);
+}
+inline void matmul_gptq_faster(int m, int n, int k, void* scale, void* bias, void* A, void* B, void* C) {
+    last_status_ref() = lutgemm_matmul_gptq(m, n, k, scale, bias, A, (const uint32_t*)B, C, nullptr);
 }
 // Dense fp16 weight into a device buffer, then waits for it (the reference synchronises too,
 // lutGEMM/src/nQWeight_fp16.cu:34).

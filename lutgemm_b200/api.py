@@ -250,3 +250,13 @@ def bcq_quantize_device(d_w, qbits, rounds=15, group_size=-1, stream=None):
     capi.check(capi.lib().lutgemm_bcq_quantize_device(_ptr(d_w), N, K, qbits, group_size, rounds, None, None, _ptr(bW),
                                                       _ptr(alpha), _stream_ptr(stream)), "bcq_quantize_device")
     return bW, alpha
+
+
+def matmul_gptq(m, n, k, scale, bias, A, B, C, stream=None):
+    """lutGEMM::matmul_gptq / matmul_gptq_faster (lutGEMM/include/kernels.h:28-33), same argument order: k is the
+    number of packed rows K * 3 / 32, scale / bias (the zero term) fp16 [n], A fp16 [m, K], B int32 [k, n], C fp16 [m, n]."""
+    capi.check(capi.lib().lutgemm_matmul_gptq(int(m), int(n), int(k), _ptr(scale), _ptr(bias), _ptr(A), _ptr(B), _ptr(C),
+                                              _stream_ptr(stream)), "matmul_gptq")
+
+
+matmul_gptq_faster = matmul_gptq

@@ -20,7 +20,7 @@ SYMBOLS = (
     "lutgemm_ipc_alloc", "lutgemm_ipc_open", "lutgemm_ipc_close", "lutgemm_ipc_free",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
-    "lutgemm_bcq_quantize", "lutgemm_bcq_quantize_device",
+    "lutgemm_bcq_quantize", "lutgemm_bcq_quantize_device", "lutgemm_matmul_gptq",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
     "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_ordered_reduction", "lutgemm_weight_device_status",
 )
@@ -87,6 +87,7 @@ def lib():
     L.lutgemm_from_python_layout.argtypes = [vp, vp, vp, ip, ip, ip, ip, vp, vp, vp]
     L.lutgemm_packer_pack.argtypes = [vp, C.c_size_t, vp]
     L.lutgemm_packer_unpack.argtypes = [vp, C.c_size_t, vp]
+    L.lutgemm_matmul_gptq.argtypes = [ip, ip, ip, vp, vp, vp, vp, vp, vp]
     L.lutgemm_bcq_quantize.argtypes = [vp, ip, ip, ip, ip, ip, vp, vp]
     L.lutgemm_bcq_quantize_device.argtypes = [vp, ip, ip, ip, ip, ip, vp, vp, vp, vp, vp]
     L.lutgemm_status_string.argtypes = [ip]

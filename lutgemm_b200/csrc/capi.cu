@@ -18,6 +18,7 @@
 #include "gemv_reg.cuh"
 #include "gemm_tc.cuh"
 #include "bcq_quantize.cuh"
+#include "gptq3.cuh"
 
 struct lutgemm_weight {
     uint32_t* bW = nullptr;
@@ -853,6 +854,26 @@ int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat) {
         int8_t* dst = flat + (size_t)i * cols;
         for (size_t j = 0; j < cols; j++) dst[j] = ((packed[j] >> i) & 1) ? 1 : -1;
     }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_matmul_gptq(int m, int n, int k_packed, const void* scale_fp16, const void* zero_fp16,
+                        const void* in_fp16, const uint32_t* mat, void* out_fp16, void* stream) {
+    if (!scale_fp16 || !zero_fp16 || !in_fp16 || !mat || !out_fp16) return LUTGEMM_ERR_NULL;
+    if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    if (n < 1 || k_packed < 3 || k_packed % 3 != 0) return LUTGEMM_ERR_SHAPE;
+    const int K = k_packed / 3 * 32;
+    const long long ctas = ((long long)n + lg::kG3Cols - 1) / lg::kG3Cols;
+    if (ctas > 0x7fffffffLL) return LUTGEMM_ERR_TOO_LARGE;
+    lg::G3Params p;
+    p.mat = mat; p.scale = (const __half*)scale_fp16; p.zero = (const __half*)zero_fp16; p.N = n; p.K = K;
+    for (int r = 0; r < m; r++) {
+        p.x = (const __half*)in_fp16 + (size_t)r * K;
+        p.y = (__half*)out_fp16 + (size_t)r * n;
+        lg::gptq3_gemv_kernel<<<(unsigned)ctas, lg::kG3Threads, 0, (cudaStream_t)stream>>>(p);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;
 }
 

@@ -7,6 +7,7 @@
  * as the timed reference baseline.  The shipped library never loads it.
  *
  * ref_dequantize_cpu   -> lutGEMM::dequantize_cpu   (lutGEMM/src/nQWeight_fp16.cu:38-59), host only
+ * ref_gpu_matmul_gptq -> lutGEMM::matmul_gptq / matmul_gptq_faster (lutGEMM/src/kernels.cu:40-54)
  * ref_gpu_*            -> nQWeight_fp16::parsing + lutGEMM::matmul on the GPU
  *                         (lutGEMM/src/nQWeight_fp16.cu:60-91, lutGEMM/src/kernels.cu:56-71);
  *                         built only into libref_gpu.so (REF_WITH_GPU).
@@ -57,6 +58,13 @@ void* ref_gpu_create(uint32_t* bW, float* alpha, float* q_bias, int K, int N, in
  * matvec kernels; legacy default stream, as the reference does. */
 void ref_gpu_matmul(void* out, void* in, void* w, int m) {
     lutGEMM::matmul(out, in, *(lutGEMM::nQWeight_fp16*)w, m);
+}
+/* The reference's 3-bit uniform kernels (lutGEMM/src/kernels.cu:40-54): k = packed rows, all pointers device or
+ * managed; they read whole 24-row x 256-column blocks without bounds checks, so call them only with
+ * K % 256 == 0 and n % 256 == 0. */
+void ref_gpu_matmul_gptq(int m, int n, int k, void* scale, void* bias, void* A, void* B, void* C, int faster) {
+    if (faster) lutGEMM::matmul_gptq_faster(m, n, k, scale, bias, A, B, C);
+    else lutGEMM::matmul_gptq(m, n, k, scale, bias, A, B, C);
 }
 int ref_gpu_last_error() { return (int)cudaGetLastError(); }
 #endif
