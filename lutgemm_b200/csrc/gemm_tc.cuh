@@ -10,13 +10,16 @@
 //   load), their scales ([groups][q][256]) and, if present, q_bias into a deep shared-memory ring (the
 //   ring is what is in flight from HBM), and the matching activation tiles x[m_pad][128 k] (128-byte
 //   swizzle) into a second ring.
+//   For up to 64 rows two warps permute every landed activation tile in place (inside each 32-k block, positions
+//   (2t, 2t + 1) take activations (t, t + 16): the order in which one shift of a packed word leaves two sign bits in
+//   a register); beyond 64 rows the kernel is MMA-bound and the expansion un-permutes its registers instead.
 //   16 expansion warps turn ONE bit plane of a step at a time into the dense fp16 operand
 //   A_b[n][k] = +-alpha_b (sign applied by XOR-ing the fp16 sign bits of two weights at a time: every
 //   operand value is exact; q_bias is one more, unsigned, plane) and write it with tcgen05.st straight
 //   into tensor memory: thread = output column = TMEM lane, 64 columns of packed fp16 pairs per 128 k.
 //   Nothing of the expanded operand touches shared memory, whose bandwidth was what limited the
 //   earlier shared-memory-operand version of this kernel (64 KB written and 96 KB read per plane and step).
-//   One lane issues tcgen05.mma.kind::f16 with the A operand in tensor memory and the activations as the
+//   Six lanes issue tcgen05.mma.kind::f16 with the A operand in tensor memory and the activations as the
 //   shared-memory B operand: M = 128 output columns, N = m_pad rows (16..128), K = 16 per instruction,
 //   two column halves, all planes accumulating into the same fp32 accumulators (TMEM lane = output column,
 //   TMEM column = activation row).  tcgen05.commit releases the operand stage / the activation slot and
@@ -51,8 +54,9 @@ constexpr int kTcMaxAStages = 3;             // operand stages in tensor memory 
 // the expansion warps' tcgen05.st traffic runs on the same SM sub-partition); several lanes on different
 // sub-partitions overlap those waits.  The lanes of a column half accumulate into the same accumulator, which the
 // expansion warps zero beforehand; the sums commute.
-constexpr int kTcMmaWarps = 2 * kTcMaxAStages, kTcTmaWarp = kTcMmaWarps, kTcFirstExpWarp = kTcMmaWarps + 1;
-constexpr int kTcThreads = (kTcExpWarps + kTcMmaWarps + 1) * 32;       // 16 + 6 + 1 warps = 736
+constexpr int kTcMmaWarps = 2 * kTcMaxAStages, kTcTmaWarp = kTcMmaWarps, kTcPermWarp = kTcMmaWarps + 1, kTcPermWarps = 2,
+              kTcFirstExpWarp = kTcPermWarp + kTcPermWarps;
+constexpr int kTcThreads = (kTcFirstExpWarp + kTcExpWarps) * 32;       // 6 + 1 + 2 + 16 warps = 800
 constexpr uint32_t kTcTmemCols = 512;
 constexpr uint32_t kTcDCol = 0;
 constexpr int kTcMaxSlots = 8;
@@ -71,6 +75,8 @@ struct TcLayout {
     int x_off, w_off, bar_off, smem_bytes;
     int d_stride;       // TMEM columns between the accumulators of the two column halves: 64 (m_pad <= 64) or 128
     int a_stages;       // operand stages in TMEM: 3 when the accumulators leave room for them, else 2
+    int permute_x;      // 1: activations are permuted in shared memory and the operand is written in shift order (m_pad <= 64,
+                        // where the expansion's instruction count is the limit); 0: the expansion un-permutes its registers
 };
 inline TcLayout tc_layout(int q, bool bias, int g, int m) {
     TcLayout L;
@@ -92,6 +98,7 @@ inline TcLayout tc_layout(int q, bool bias, int g, int m) {
     L.smem_bytes = kTcSmemTotal;
     L.d_stride = L.m_pad <= 64 ? 64 : 128;
     L.a_stages = L.m_pad <= 64 ? 3 : 2;                    // 2 * d_stride + 128 * a_stages = 512 columns
+    L.permute_x = L.m_pad <= 64 ? 1 : 0;
     return L;
 }
 
@@ -112,6 +119,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
                  " [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -182,10 +190,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const uint32_t bar_wempty = bar0 + 8 * kTcMaxSlots;
     const uint32_t bar_xfull = bar0 + 16 * kTcMaxSlots;
     const uint32_t bar_xempty = bar0 + 24 * kTcMaxSlots;
-    const uint32_t bar_afull = bar0 + 32 * kTcMaxSlots;           // kTcMaxAStages
+    const uint32_t bar_xready = bar0 + 32 * kTcMaxSlots;          // activation slot permuted, kTcMaxSlots
+    const uint32_t bar_afull = bar0 + 40 * kTcMaxSlots;           // kTcMaxAStages
     const uint32_t bar_aempty = bar_afull + 8 * kTcMaxAStages;
     const uint32_t bar_acc = bar_aempty + 8 * kTcMaxAStages;
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L.bar_off + 32 * kTcMaxSlots + 16 * kTcMaxAStages + 16);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L.bar_off + 40 * kTcMaxSlots + 16 * kTcMaxAStages + 16);
     const uint32_t a_col0 = 2u * (uint32_t)L.d_stride;             // first operand column in tensor memory
     const int nA = L.a_stages;
     int* s_flag = reinterpret_cast<int*>(s_tmem + 2);
@@ -206,6 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             mbar_init(bar_wempty + 8 * s, kTcExpWarps);
             mbar_init(bar_xfull + 8 * s, 1);
             mbar_init(bar_xempty + 8 * s, kTcMmaWarps);
+            mbar_init(bar_xready + 8 * s, kTcPermWarps);
         }
         for (int s = 0; s < kTcMaxAStages; s++) {
             mbar_init(bar_afull + 8 * s, kTcExpWarps);
@@ -272,21 +282,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 }
 #pragma unroll
                 for (int u = 0; u < 2; u++) {
-                    // two weights per register: element t (low half) and t + 16 (high half) of the packed word;
-                    // bit set -> +alpha, bit clear -> -alpha (sign bit flipped where the bit is 0); q_bias plane: no sign
+                    // two weights per register: element t (low half) and t + 16 (high half) of the packed word: register t
+                    // goes to TMEM column t, i.e. k-positions (2t, 2t + 1) of the block, which is where the permute warp
+                    // has put activations t and t + 16.  Bit set -> +alpha, bit clear -> -alpha (sign bit flipped where
+                    // the bit is 0); q_bias plane: no sign
                     uint32_t nat[16];
                     if (b < Q) {
-                        uint32_t h[16];
 #pragma unroll
                         for (int t = 0; t < 16; t++) {
                             const uint32_t sh = (t == 15) ? w[u] : (w[u] << (15 - t));
-                            h[t] = a[u] ^ (~sh & 0x80008000u);
+                            nat[t] = a[u] ^ (~sh & 0x80008000u);
                         }
-                        // natural k order: (0,1), (2,3), ... then (16,17), ...
+                        if (!L.permute_x) {
+                            // activations in natural order: pairs (0,1), (2,3), ... then (16,17), ...
+                            uint32_t h[16];
 #pragma unroll
-                        for (int jj = 0; jj < 8; jj++) {
-                            nat[jj] = prmt_b32(h[2 * jj], h[2 * jj + 1], 0x5410u);
-                            nat[jj + 8] = prmt_b32(h[2 * jj], h[2 * jj + 1], 0x7632u);
+                            for (int t = 0; t < 16; t++) h[t] = nat[t];
+#pragma unroll
+                            for (int jj = 0; jj < 8; jj++) {
+                                nat[jj] = prmt_b32(h[2 * jj], h[2 * jj + 1], 0x5410u);
+                                nat[jj + 8] = prmt_b32(h[2 * jj], h[2 * jj + 1], 0x7632u);
+                            }
                         }
                     } else {
 #pragma unroll
@@ -343,7 +359,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (++xs == L.x_slots) { xs = 0; xround++; }
             __syncwarp();
         }
-    } else {
+    } else if (warp >= kTcPermWarp) {                      // the permute warps; idle when the layout does not ask for them
+        // ---------------- activation permute: inside every 32-k block, positions (2t, 2t + 1) <- activations (t, t + 16) --------
+        // (the order in which the expansion's shift leaves two weights in a register; permuting the few activations
+        // once per step costs far less than un-permuting every expanded operand register)
+        int xs = 0, xround = 0;
+        for (int j = 0; j < (L.permute_x ? nsteps : 0); j++) {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_xfull + 8 * xs, xround & 1))) { timed_out = true; break; }
+            unsigned char* slot = smem + L.x_off + xs * L.x_slot_bytes;
+            const int tasks = 4 * p.m;                               // (sub-tile, row < m, 32-k block); rows >= m are zero
+            for (int tk = (warp - kTcPermWarp) * 32 + lane; tk < tasks; tk += 32 * kTcPermWarps) {
+                const int blk = tk & 1, sub = (tk >> 1) & 1, r = tk >> 2;
+                unsigned char* row = slot + sub * L.x_sub_bytes + (r >> 3) * 1024 + (r & 7) * 128;
+                uint4 in[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) in[i] = *reinterpret_cast<const uint4*>(row + (((4 * blk + i) ^ (r & 7)) << 4));
+                const uint32_t v[16] = {in[0].x, in[0].y, in[0].z, in[0].w, in[1].x, in[1].y, in[1].z, in[1].w,
+                                        in[2].x, in[2].y, in[2].z, in[2].w, in[3].x, in[3].y, in[3].z, in[3].w};
+                uint32_t o[16];
+#pragma unroll
+                for (int t = 0; t < 16; t++) o[t] = prmt_b32(v[t >> 1], v[(t >> 1) + 8], (t & 1) ? 0x7632u : 0x5410u);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    *reinterpret_cast<uint4*>(row + (((4 * blk + i) ^ (r & 7)) << 4)) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+            fence_proxy_async_smem();                                // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_xready + 8 * xs);
+            if (++xs == L.x_slots) { xs = 0; xround++; }
+        }
+    } else if (warp < kTcMmaWarps) {
         // ---------------- MMA issue: warp w takes column half w & 1 of the stages t with t mod nA == w >> 1 ----------------
         // (whole warp in the loop, lane 0 issues; see the TMA warp)
         const int hN = warp & 1, par = warp >> 1;          // par >= nA: nothing to issue, but the commits below still arrive
@@ -354,7 +399,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         int t = 0, tmod = 0;                           // running stage index (step * P + plane) and t mod nA
         int sround = 0, xs = 0, xround = 0;
         for (int j = 0; j < nsteps && !timed_out; j++) {
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_xfull + 8 * xs, xround & 1))) { timed_out = true; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded((L.permute_x ? bar_xready : bar_xfull) + 8 * xs, xround & 1))) { timed_out = true; break; }
 #pragma unroll 1
             for (int b = 0; b < P; b++, t++, tmod = (tmod + 1 == nA) ? 0 : tmod + 1) {
                 if (tmod != par) continue;

@@ -262,6 +262,26 @@ def test_device_packer_and_converter_bit_exact():
     assert np.array_equal(qb_d.cpu().numpy(), qb_h.astype(np.float16))
 
 
+def test_host_call_with_page_locked_buffers_reads_fresh_inputs():
+    """The host-buffer call with page-locked buffers reused across calls: every call must see what the host wrote just
+    before it, and pageable buffers must give the same numbers."""
+    N, K, q, g = 2048, 4096, 3, 128
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=21, with_bias=True)
+    w = L.nQWeight_fp16(bW, alpha, K, N, q, False, K // g, qb)
+    xin = torch.empty((1, K), dtype=torch.float16).pin_memory()
+    yout = torch.empty((1, N), dtype=torch.float16).pin_memory()
+    for seed in (1, 2, 3):
+        x = synth.activations(1, K, seed=seed)
+        xin.numpy()[:] = x
+        yout.numpy()[:] = 0
+        L.matmul_host(yout.numpy(), xin.numpy(), w, 1)
+        ref = oracle_y(bW, alpha, qb, g, x)
+        check(yout.numpy().astype(np.float32), ref, K, f"pinned matmul_host, input {seed}")
+        y_pageable = np.empty((1, N), np.float16)
+        L.matmul_host(y_pageable, x.copy(), w, 1)
+        assert np.abs(y_pageable.astype(np.float32) - yout.numpy().astype(np.float32)).max() <= 2e-3 * np.abs(ref).max()
+
+
 def test_host_buffer_call_and_borrowed_device_container():
     N, K, q, g = 1024, 1024, 3, 128
     bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=8, with_bias=True)
