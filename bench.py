@@ -44,8 +44,8 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = 63966976
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
                     help="reference: the reference's CPU path; reference-gpu (helper leg): the reference's own CUDA kernels, "
                          "compiled for sm_100a into oracle/_ref/libref_gpu.so, on the same matvec")
@@ -598,6 +598,17 @@ def run_ours(a):
     sec = ms / 1e3
     value = world * a.steps * rot * B / sec / 1e9
     us_per_gemv = sec / (a.steps * rot) * 1e6
+    # spread of single steps: 200 replays timed one by one (outside the timed region above)
+    spread = None
+    if rank == 0:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+        for s0, s1 in evs:
+            s0.record()
+            run_step()
+            s1.record()
+        torch.cuda.synchronize()
+        per = sorted(s0.elapsed_time(s1) * 1e3 / rot for s0, s1 in evs)
+        spread = {"median": per[len(per) // 2], "min": per[0], "max": per[-1], "steps_timed_singly": len(per)}
 
     # end to end through the host-buffer entry point
     e2e = None
@@ -645,6 +656,7 @@ def run_ours(a):
                    "parallelism": f"independent layers per rank x{world}",
                    "launch": "python" if graph is None else "cuda graph of one step, replayed"},
         "us_per_matvec": us_per_gemv,
+        "us_per_matvec_single_steps": spread,
         "packed_weight_GBps": a.n * a.k * a.q / 8 / (us_per_gemv * 1e-6) / 1e9,
         "pct_of_8TBps_nominal": 100.0 * achieved / 8000.0,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
