@@ -318,3 +318,30 @@ def test_bad_runtime_arguments_return_status():
     L.matmul(out, x, w, 1)
     assert lib.lutgemm_kernel_launch_count() == n0 + 1
     w.close()
+
+
+def _random_config(rng):
+    g = int(rng.choice([32, 64, 96, 128, 256, 512, 1024]))
+    K = g * int(rng.integers(1, max(2, 6144 // g)))
+    N = int(rng.choice([8, 4, 2, 1])) * int(rng.integers(1, 700))
+    q = int(rng.integers(1, 9))
+    m = int(rng.choice([1, 1, 2, 3, 4, 5, 16, 17, 33, 64, 100, 128, 131]))
+    bias = bool(rng.integers(0, 2))
+    return N, K, q, g, m, bias
+
+
+@pytest.mark.parametrize("seed", list(range(32)))
+def test_random_configurations(seed):
+    """Seeded random (N, K, q, g, m, q_bias): whatever kernel the dispatch picks (TMA-fed or register-fed matvec, generic
+    fallback, tensor-core batched kernel with either operand order) must agree with the fp32 host reference."""
+    rng = np.random.default_rng(1000 + seed)
+    N, K, q, g, m, bias = _random_config(rng)
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=seed, with_bias=bias, signed_alpha=bool(seed & 1),
+                                    alpha_std=min(0.02, 0.6 / np.sqrt(K * q)))
+    x = synth.activations(m, K, seed=seed + 7)
+    ref = oracle_y(bW, alpha, qb, g, x)
+    y32 = run_matmul(bW, alpha, qb, g, x, f32=True)
+    y16 = run_matmul(bW, alpha, qb, g, x)
+    what = f"N={N} K={K} q={q} g={g} m={m} bias={bias}"
+    check(y32, ref, K, what + " fp32 out", fp32_out=True)
+    check(y16.astype(np.float32), ref, K, what)
