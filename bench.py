@@ -50,6 +50,7 @@ def parse():
                     help="reference: the reference's CPU path; reference-gpu (helper leg): the reference's own CUDA kernels, "
                          "compiled for sm_100a into oracle/_ref/libref_gpu.so, on the same matvec")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference-CUDA-kernel leg of the default run")
+    ap.add_argument("--reference-gpu", action="store_true", help="with --m > 1: also time the reference's batched path (dequantise + cuBLAS)")
     ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "stack", "quantize", "gptq"],
                     help="gemv: the headline matvec; stack: tensor-parallel decoder linear stack; auto: gemv on 1 GPU, stack on more; "
                          "quantize: the BCQ quantiser (greedy + --rounds refinements) on an [n, k] fp32 layer, a side line; "
@@ -205,8 +206,9 @@ def run_reference_gpu(a):
     import ctypes as C
     import torch
     so = os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so")
-    if not os.path.exists(so) or a.m != 1:
-        print(json.dumps({"reference_gpu": None, "why": "oracle/_ref/libref_gpu.so not built" if a.m == 1 else "m > 1"}))
+    if not os.path.exists(so) or (a.m > 1 and a.q > 4):
+        print(json.dumps({"reference_gpu": None, "why": "oracle/_ref/libref_gpu.so not built" if a.q <= 4 or a.m == 1 else
+                          "the reference's batched path dequantises nothing for q > 4"}))
         return
     R = C.CDLL(so)
     R.ref_gpu_create.restype = C.c_void_p
@@ -219,30 +221,32 @@ def run_reference_gpu(a):
         bW, alpha, qb = synth.bcq_layer(a.n, a.k, a.q, a.g, seed=synth.seed_for("bench", a.n, a.k, a.q, i), with_bias=a.bias)
         keep.append((bW, alpha, qb))
         ws.append(R.ref_gpu_create(bW.ctypes.data, alpha.ctypes.data, None if qb is None else qb.ctypes.data, a.k, a.n, a.q, a.k // a.g))
-    x_host = synth.activations(1, a.k, seed=123)
+    x_host = synth.activations(a.m, a.k, seed=123)
     x = torch.from_numpy(x_host.view(np.int16)).cuda().view(torch.float16)
-    y = torch.empty((1, a.n), dtype=torch.float16, device="cuda")
+    y = torch.empty((a.m, a.n), dtype=torch.float16, device="cuda")
     for _ in range(3):
         for w in ws:
-            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, 1)
+            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, a.m)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     steps = max(1, min(a.steps, 20))
     e0.record()
     for _ in range(steps):
         for w in ws:
-            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, 1)
+            R.ref_gpu_matmul(y.data_ptr(), x.data_ptr(), w, a.m)
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (steps * rot)
-    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, 1, a.bias)
+    B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, a.m, a.bias)
     # accuracy of the reference kernel on the last weight set, against the fp32 host evaluation
     from oracle import oracle
     bW, alpha, qb = keep[-1]
     ref = oracle.bcq_matmul_fp32(x_host, bW, alpha.astype(np.float16), None if qb is None else qb.astype(np.float16), a.g)
     got = y.float().cpu().numpy()
     print(json.dumps({"reference_gpu": {"us_per_matvec": us, "value": B / (us * 1e-6) / 1e9, "unit": UNIT,
-                                        "kernel": "_nqmv_bias<32>" if a.bias else "_nqmv<64>", "launches_per_matvec": 2,
+                                        "kernel": ("_nqmv_bias<32>" if a.bias else "_nqmv<64>") if a.m == 1 else
+                                                  "_dequantize_t + cublasGemmEx (q_bias ignored, two device synchronisations)",
+                                        "launches_per_matvec": 2,
                                         "mae_vs_fp32_host": float(np.abs(got - ref).mean())}}), flush=True)
 
 
@@ -670,11 +674,12 @@ def run_ours(a):
     if a.m > 1:
         line["tensor_flops_per_matmul"] = 2.0 * a.m * a.n * a.k * (a.q + (1 if a.bias else 0))
         line["tensor_TFLOPs"] = line["tensor_flops_per_matmul"] / (us_per_gemv * 1e-6) / 1e12
-    if world == 1 and a.m == 1 and not a.no_reference_gpu and not a.no_cpu_baseline:
-        # the reference's own CUDA kernels on the same matvec, in a child process (a fault there cannot take this run down)
+    if world == 1 and not a.no_reference_gpu and (a.m == 1 and not a.no_cpu_baseline or a.m > 1 and a.reference_gpu):
+        # the reference's own CUDA code on the same call, in a child process (a fault there cannot take this run down):
+        # m = 1 its LUT kernels, m > 1 (on request, --reference-gpu) its dequantise + cuBLAS path
         try:
             child = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--n", str(a.n), "--k", str(a.k),
-                                    "--q", str(a.q), "--g", str(a.g), "--rot", str(rot), "--steps", "10"] + (["--bias"] if a.bias else []),
+                                    "--q", str(a.q), "--g", str(a.g), "--m", str(a.m), "--rot", str(rot), "--steps", "10"] + (["--bias"] if a.bias else []),
                                    capture_output=True, text=True, timeout=180)
             rows = [l for l in child.stdout.splitlines() if l.startswith("{")]
             line["reference_gpu"] = json.loads(rows[-1])["reference_gpu"] if rows else None

@@ -51,11 +51,16 @@ void ref_dequantize_cpu(const uint32_t* bW, const uint16_t* alpha_h, int K, int 
 void* ref_gpu_create(uint32_t* bW, float* alpha, float* q_bias, int K, int N, int q, int num_groups) {
     auto* w = new lutGEMM::nQWeight_fp16();
     w->parsing(bW, alpha, K, N, q, false, num_groups, q_bias);
+    /* parsing() computes group_size from kSize before kSize is set (lutGEMM/src/nQWeight_fp16.cu:62-63), leaving it
+     * indeterminate; the m = 1 kernels never read it, but the batched path's _dequantize_t divides by it
+     * (lutGEMM/src/cuda/kernels/dequant_fp16.hpp:66), so the public field is given the value it was meant to have. */
+    w->group_size = K / num_groups;
     cudaDeviceSynchronize();
     return (void*)w;
 }
-/* out, in: device (or managed) fp16 pointers.  m == 1 runs the reference LUT
- * matvec kernels; legacy default stream, as the reference does. */
+/* out, in: device (or managed) fp16 pointers.  m == 1 runs the reference LUT matvec kernels, m > 1 its
+ * dequantise-to-scratch + cuBLAS path (q <= 4 only: beyond that its dequantiser launches nothing,
+ * lutGEMM/src/cuda/kernels/dequant_fp16.hpp:102-105); legacy default stream, as the reference does. */
 void ref_gpu_matmul(void* out, void* in, void* w, int m) {
     lutGEMM::matmul(out, in, *(lutGEMM::nQWeight_fp16*)w, m);
 }
