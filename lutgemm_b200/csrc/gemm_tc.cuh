@@ -436,28 +436,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (!ok) atomicExch(p.status, kStatusTcTimeout);
         tc_fence_after_sync();
         const int lq = warp & 3, gi = (warp - kTcFirstExpWarp) >> 2, hN = gi & 1, hK = gi >> 1;
-        const int n = n0 + hN * 128 + lq * 32 + lane;
         const uint32_t t_src = tmem_base + ((uint32_t)(lq * 32) << 16) + kTcDCol + (uint32_t)(hN * L.d_stride);
+        // A tcgen05.ld leaves lane = output column, register = activation row.  Each 16 x 32 block is turned through a
+        // per-warp scratch in shared memory (the activation ring, idle once the accumulators are complete; rows padded to
+        // 33 floats: no bank conflicts either way) so that a lane holds 4 consecutive columns of one row: vector
+        // reductions / 128-bit stores, a quarter of the L2 transactions of scalar ones.
+        float* scratch = reinterpret_cast<float*>(smem + L.x_off) + (warp - kTcFirstExpWarp) * (16 * 33);
+        const int ncol0 = n0 + hN * 128 + lq * 32;
         for (int c = hK; 16 * c < p.m && ok; c += 2) {     // 16 activation rows per tcgen05.ld; warp-uniform
             uint32_t r[16];
             tmem_ld_x16(t_src + 16u * (uint32_t)c, r);
             tmem_ld_wait();
-            if (n < N) {
 #pragma unroll
-                for (int jj = 0; jj < 16; jj++) {
-                    const int mrow = 16 * c + jj;
-                    if (mrow < p.m) {
-                        const float v = __uint_as_float(r[jj]);
-                        const size_t o = (size_t)mrow * rowN + n;
-                        if (split) {
-                            atomicAdd(p.partial + o, v);           // result unused: a reduction performed in L2
-                        } else {
-                            if (p.y32) p.y32[o] = v;
-                            if (p.y16) p.y16[o] = __float2half_rn(v);
+            for (int jj = 0; jj < 16; jj++) scratch[jj * 33 + lane] = __uint_as_float(r[jj]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = (lane >> 3) + 4 * i, col4 = (lane & 7) * 4;
+                const float* src = scratch + row * 33 + col4;
+                const float4 v = make_float4(src[0], src[1], src[2], src[3]);
+                const int mrow = 16 * c + row, n = ncol0 + col4;
+                if (mrow < p.m && n < N) {                 // N % 8 == 0 on this path: whole groups of four columns
+                    const size_t o = (size_t)mrow * rowN + n;
+                    if (split) {
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + o), "f"(v.x), "f"(v.y),
+                                     "f"(v.z), "f"(v.w) : "memory");
+                    } else {
+                        if (p.y32) *reinterpret_cast<float4*>(p.y32 + o) = v;
+                        if (p.y16) {
+                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                            uint2 h2;
+                            h2.x = *reinterpret_cast<uint32_t*>(&lo);
+                            h2.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(p.y16 + o) = h2;
                         }
                     }
                 }
             }
+            __syncwarp();
         }
         tc_fence_before_sync();
     }
