@@ -339,7 +339,17 @@ int launch_gemm_tc_q(const lutgemm_weight* w, const CUtensorMap& tmX, const lg::
         LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemTotal));
         if (dev < 64) configured[dev][bias] = true;
     }
-    kern<<<grid, lg::kTcThreads, p.L.smem_bytes, st>>>(tmX, w->tmWtc, w->tmAtc, w->tmQtc, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(lg::kTcThreads);
+    cfg.dynamicSmemBytes = (size_t)p.L.smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    LG_CUDA(cudaLaunchKernelEx(&cfg, kern, tmX, w->tmWtc, w->tmAtc, w->tmQtc, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;

@@ -233,6 +233,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = *s_tmem;
     bool timed_out = false;
+    // Launched with programmatic stream serialization: the packed planes and scales are never written by a kernel, so
+    // their stream and the expansion into tensor memory start while the previous kernel of the stream drains; the
+    // activations, the split-k workspace and the outputs are touched only after griddepcontrol.wait.
+    pdl_launch_dependents();
 
     if (warp >= kTcFirstExpWarp) {
         // ---------------- expansion: packed planes (shared memory) -> dense fp16 operand (tensor memory) ----------------
@@ -347,6 +351,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
             if (++ws == L.w_slots) { ws = 0; wround++; }
 
+            if (j == 0) pdl_wait_prior_grids();                      // the activations may come from the previous kernel
             if (xround > 0) {
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_xempty + 8 * xs, (xround - 1) & 1))) { timed_out = true; break; }
             }
@@ -427,6 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (lane == 0) umma_commit(bar_acc);               // this warp's share of the accumulators is complete
         __syncwarp();
     }
+    pdl_wait_prior_grids();                  // before any store to global memory (returns at once if already passed)
     if (timed_out) atomicExch(p.status, kStatusTcTimeout);
 
     // ---------------- epilogue: TMEM lane = output column, TMEM column = activation row ----------------
