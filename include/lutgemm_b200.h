@@ -216,7 +216,8 @@ int lutgemm_matmul_gptq(int m, int n, int k_packed, const void* scale_fp16, cons
  * :130-157, find_B_torch :165-188, batch_cg_torch :190-206) for its default unweighted case (exponent 0,
  * clipping 1, pruning 0).  w float [N][K] (output rows, groups of `group_size` consecutive input features;
  * group_size <= 0: one group per row); `rounds` refinements after the greedy start (the reference's default is
- * 15; ignored for q == 1).  One warp quantises one group, so group_size <= 1024.  Outputs, each optional
+ * 15; ignored for q == 1).  One warp quantises a group of up to 1024 weights, one CTA a wider one (up to 65536).
+ * Outputs, each optional
  * (NULL to skip) in the device form: the quantiser's own layout alpha [N][G][q] / binary int8 [N][G][g][q]
  * in {-1, 0, +1} (0 only where the greedy start met an exactly zero residual), and the container layout of this
  * library, bW [K/32][q][N] and alpha fp16 [G][q][N] (needs group_size % 32 == 0; a zero code packs as -1),

@@ -8,7 +8,7 @@
 //                                          both denominators), |alpha| sorted descending, then every weight takes the
 //                                          nearest of the 2^q levels sum_i +-alpha_i (examples/bcq.py:165-188: levels
 //                                          sorted, q bisection steps on midpoints, `w < mid` goes left).
-// Here a group never leaves its warp: the weights stay in registers (lane l holds elements l, l + 32, ...), the
+// Here a group up to 1024 wide never leaves its warp (wider ones take a CTA, see the end of this file): the weights stay in registers (lane l holds elements l, l + 32, ...), the
 // q x q system is accumulated with warp reductions and solved redundantly by every lane, the 2^q levels are rank-sorted
 // in shared memory.  Output in the quantiser's layout (alpha [N][G][q] fp32, binary int8 [N][G][g][q]) and/or directly
 // in the matmul's container layout (bW uint32 [K/32][q][N] by warp ballots, alpha fp16 [G][q][N]).
@@ -226,6 +226,214 @@ bcq_quantize_kernel(const BqParams p) {
             for (int i = 0; i < q; i++) {
                 const uint32_t word = __ballot_sync(0xffffffffu, valid && ((code[e] >> i) & 1u));
                 if (lane == 0) p.bW[((size_t)((gi * g) / 32 + e) * q + i) * p.N + n] = word;
+            }
+        }
+    }
+}
+
+// ---- groups wider than 1024 (the reference's default is one group per row): one CTA per (row, group) ----
+// Same arithmetic; the codes live in shared memory (2 bytes per weight), the weights are re-read from global memory
+// (L2) twice per round, sums go through warp shuffles and a shared-memory stage, and warp 0 solves for alpha and
+// sorts the levels.
+constexpr int kBqBlockThreads = 256;
+
+__device__ __forceinline__ float block_sum_f(float v, float* s_stage, int tid) {
+    v = warp_sum_f(v);
+    __syncthreads();                                   // s_stage free
+    if ((tid & 31) == 0) s_stage[tid >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kBqBlockThreads / 32; w++) t += s_stage[w];
+    return t;
+}
+
+__global__ void __launch_bounds__(kBqBlockThreads)
+bcq_quantize_block_kernel(const BqParams p) {
+    extern __shared__ unsigned short s_code[];         // [g]: bits 0..7 "+1" per plane, 8..15 "non-zero" per plane
+    __shared__ float s_stage[kBqBlockThreads / 32];
+    __shared__ float s_acc[kBqMaxQ + kBqMaxQ * kBqMaxQ];
+    __shared__ float s_alpha[kBqMaxQ];
+    __shared__ float s_v[1 << kBqMaxQ];
+    __shared__ float s_vs[1 << kBqMaxQ];
+    __shared__ unsigned char s_ind[1 << kBqMaxQ];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int G = p.K / p.g, g = p.g, q = p.q;
+    const int n = blockIdx.x / G, gi = blockIdx.x % G;
+    const float* wg = p.w + (size_t)n * p.K + (size_t)gi * g;
+    if (tid < kBqMaxQ) s_alpha[tid] = 0.f;
+    for (int idx = tid; idx < g; idx += kBqBlockThreads) s_code[idx] = 0;
+    __syncthreads();
+
+    auto residual = [&](int idx, int upto) {           // w - sum_{j < upto} alpha_j b_j
+        float r = wg[idx];
+        const uint32_t c = s_code[idx];
+        for (int j = 0; j < upto; j++) r -= s_alpha[j] * code_sign(c, j);
+        return r;
+    };
+    // ---- greedy ----
+    for (int i = 0; i < q; i++) {
+        float s = 0.f;
+        for (int idx = tid; idx < g; idx += kBqBlockThreads) s += fabsf(residual(idx, i));
+        float a = block_sum_f(s, s_stage, tid) / (float)g;
+        if (a != a) a = 0.f;
+        for (int idx = tid; idx < g; idx += kBqBlockThreads) {
+            const float r = residual(idx, i);
+            unsigned short c = s_code[idx];
+            if (r > 0.f) c |= (unsigned short)(1u << i);
+            if (r != 0.f) c |= (unsigned short)(1u << (8 + i));
+            s_code[idx] = c;
+        }
+        __syncthreads();
+        if (tid == 0) s_alpha[i] = a;
+        __syncthreads();
+    }
+    // ---- alternating refinement ----
+    if (q > 1) {
+        const int nlev = 1 << q;
+        for (int round = 0; round < p.rounds; round++) {
+            // B^T w and the Gram matrix, reduced over the block
+            float btw[kBqMaxQ];
+            int cov[kBqMaxQ * (kBqMaxQ + 1) / 2];
+#pragma unroll
+            for (int i = 0; i < kBqMaxQ; i++) btw[i] = 0.f;
+#pragma unroll
+            for (int i = 0; i < kBqMaxQ * (kBqMaxQ + 1) / 2; i++) cov[i] = 0;
+            for (int idx = tid; idx < g; idx += kBqBlockThreads) {
+                const float wv = wg[idx];
+                const uint32_t c = s_code[idx];
+                int t = 0;
+#pragma unroll
+                for (int i = 0; i < kBqMaxQ; i++) {
+                    const float bi = i < q ? code_sign(c, i) : 0.f;
+                    btw[i] += bi * wv;
+#pragma unroll
+                    for (int j = i; j < kBqMaxQ; j++, t++) cov[t] += (int)(bi * (j < q ? code_sign(c, j) : 0.f));
+                }
+            }
+            {
+                int t = 0;
+                for (int i = 0; i < kBqMaxQ; i++) {
+                    const float sb = block_sum_f(i < q ? btw[i] : 0.f, s_stage, tid);
+                    if (tid == 0) s_acc[i] = sb;
+                    for (int j = i; j < kBqMaxQ; j++, t++) {
+                        if (i < q && j < q) {
+                            const float sc = block_sum_f((float)cov[t], s_stage, tid);      // integer counts below 2^24: exact
+                            if (tid == 0) { s_acc[kBqMaxQ + i * kBqMaxQ + j] = sc; s_acc[kBqMaxQ + j * kBqMaxQ + i] = sc; }
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            if (tid < 32) {
+                // warp 0: q steps of conjugate gradient from the current alpha, |alpha| descending, levels rank-sorted
+                float x[kBqMaxQ], r[kBqMaxQ], pp[kBqMaxQ], Ap[kBqMaxQ], al[kBqMaxQ];
+                float rtr_new = 0.f;
+#pragma unroll
+                for (int i = 0; i < kBqMaxQ; i++) al[i] = s_alpha[i];
+#pragma unroll
+                for (int i = 0; i < kBqMaxQ; i++) {
+                    x[i] = al[i];
+                    float sdot = 0.f;
+#pragma unroll
+                    for (int j = 0; j < kBqMaxQ; j++) if (i < q && j < q) sdot += s_acc[kBqMaxQ + i * kBqMaxQ + j] * al[j];
+                    r[i] = i < q ? s_acc[i] - sdot : 0.f;
+                    pp[i] = r[i];
+                    rtr_new += r[i] * r[i];
+                }
+                for (int it = 0; it < q; it++) {
+                    const float rtr = rtr_new;
+                    float pAp = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kBqMaxQ; i++) {
+                        float sdot = 0.f;
+#pragma unroll
+                        for (int j = 0; j < kBqMaxQ; j++) if (i < q && j < q) sdot += s_acc[kBqMaxQ + i * kBqMaxQ + j] * pp[j];
+                        Ap[i] = i < q ? sdot : 0.f;
+                        pAp += pp[i] * Ap[i];
+                    }
+                    const float a = rtr / (pAp + 1e-6f);
+                    rtr_new = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kBqMaxQ; i++) {
+                        x[i] += a * pp[i];
+                        r[i] -= a * Ap[i];
+                        rtr_new += r[i] * r[i];
+                    }
+                    const float beta = rtr_new / (rtr + 1e-6f);
+#pragma unroll
+                    for (int i = 0; i < kBqMaxQ; i++) pp[i] = r[i] + beta * pp[i];
+                }
+#pragma unroll
+                for (int i = 0; i < kBqMaxQ; i++) al[i] = i < q ? fabsf(x[i]) : -1.f;
+#pragma unroll
+                for (int i = 1; i < kBqMaxQ; i++) {
+#pragma unroll
+                    for (int j = i; j > 0; j--) {
+                        if (al[j] > al[j - 1]) { const float t2 = al[j]; al[j] = al[j - 1]; al[j - 1] = t2; }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kBqMaxQ; i++) if (i >= q) al[i] = 0.f;
+                __syncwarp();
+                if (lane < kBqMaxQ) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kBqMaxQ; i++) if (i == lane) a = al[i];
+                    s_alpha[lane] = a;
+                }
+                for (int c = lane; c < nlev; c += 32) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kBqMaxQ; i++) if (i < q) v += ((c >> (q - 1 - i)) & 1) ? -al[i] : al[i];
+                    s_v[c] = v;
+                }
+                __syncwarp();
+                for (int c = lane; c < nlev; c += 32) {
+                    const float v = s_v[c];
+                    int rank = 0;
+                    for (int d = 0; d < nlev; d++) {
+                        const float u = s_v[d];
+                        rank += (u < v || (u == v && d < c)) ? 1 : 0;
+                    }
+                    s_vs[rank] = v;
+                    s_ind[rank] = (unsigned char)c;
+                }
+            }
+            __syncthreads();
+            for (int idx = tid; idx < g; idx += kBqBlockThreads) {
+                const float wv = wg[idx];
+                int left = 0, right = nlev - 1;
+                for (int it = 0; it < q; it++) {
+                    const int ml = (left + right - 1) / 2, mr = ml + 1;
+                    const float mid = (s_vs[ml] + s_vs[mr]) / 2.f;
+                    if (wv < mid) right = ml; else left = mr;
+                }
+                const uint32_t c = s_ind[left];
+                uint32_t pos = 0u;
+                for (int i = 0; i < q; i++) pos |= (((c >> (q - 1 - i)) & 1u) ^ 1u) << i;
+                s_code[idx] = (unsigned short)(pos | (((1u << q) - 1u) << 8));
+            }
+            __syncthreads();
+        }
+    }
+    // ---- outputs ----
+    if (tid < q) {
+        if (p.alpha_py) p.alpha_py[((size_t)n * G + gi) * q + tid] = s_alpha[tid];
+        if (p.alpha_k) p.alpha_k[((size_t)gi * q + tid) * p.N + n] = __float2half_rn(s_alpha[tid]);
+    }
+    const int g_pad = (g + 31) / 32 * 32;
+    for (int idx = tid; idx < g_pad; idx += kBqBlockThreads) {        // whole warps walk whole 32-element words
+        const bool valid = idx < g;
+        const uint32_t c = valid ? s_code[idx] : 0u;
+        if (p.binary_py && valid) {
+            signed char* dst = p.binary_py + (((size_t)n * G + gi) * g + idx) * q;
+            for (int i = 0; i < q; i++) dst[i] = (signed char)code_sign(c, i);
+        }
+        if (p.bW) {                                         // g % 32 == 0 here; a zero code packs as -1
+            for (int i = 0; i < q; i++) {
+                const uint32_t word = __ballot_sync(0xffffffffu, valid && ((c >> i) & 1u));
+                if (lane == 0) p.bW[((size_t)((gi * g + idx) / 32) * q + i) * p.N + n] = word;
             }
         }
     }

@@ -893,7 +893,7 @@ int lutgemm_bcq_quantize_device(const float* d_w, int N, int K, int q, int group
     if (!d_w || (!d_alpha_py && !d_binary_py && !d_bW && !d_alpha_fp16)) return LUTGEMM_ERR_NULL;
     if (q < 1 || q > lg::kBqMaxQ) return LUTGEMM_ERR_BITS;
     const int g = group_size > 0 ? group_size : K;
-    if (N < 1 || K < 1 || rounds < 0 || K % g != 0 || g > 1024) return LUTGEMM_ERR_SHAPE;
+    if (N < 1 || K < 1 || rounds < 0 || K % g != 0 || g > 65536) return LUTGEMM_ERR_SHAPE;
     if ((d_bW || d_alpha_fp16) && (g % 32 != 0)) return LUTGEMM_ERR_SHAPE;
     lg::BqParams p;
     p.w = d_w; p.N = N; p.K = K; p.g = g; p.q = q; p.rounds = rounds;
@@ -904,7 +904,20 @@ int lutgemm_bcq_quantize_device(const float* d_w, int N, int K, int q, int group
     cudaStream_t st = (cudaStream_t)stream;
     if (g <= 128) lg::bcq_quantize_kernel<4><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
     else if (g <= 256) lg::bcq_quantize_kernel<8><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
-    else lg::bcq_quantize_kernel<32><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
+    else if (g <= 1024) lg::bcq_quantize_kernel<32><<<(unsigned)ctas, lg::kBqWarps * 32, 0, st>>>(p);
+    else {
+        // one CTA per group, its codes (2 bytes per weight) in dynamic shared memory
+        if (groups > 0x7fffffffLL) return LUTGEMM_ERR_TOO_LARGE;
+        const size_t smem = (size_t)g * sizeof(unsigned short);
+        static bool configured[64] = {};
+        int dev = 0;
+        LG_CUDA(cudaGetDevice(&dev));
+        if (dev >= 64 || !configured[dev]) {
+            LG_CUDA(cudaFuncSetAttribute(lg::bcq_quantize_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+            if (dev < 64) configured[dev] = true;
+        }
+        lg::bcq_quantize_block_kernel<<<(unsigned)groups, lg::kBqBlockThreads, smem, st>>>(p);
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;

@@ -57,7 +57,9 @@ def test_device_quantiser_matches_reference_vectors(name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("N,K,g,q,rounds", [(64, 1024, 128, 3, 15), (48, 768, 32, 4, 6), (8, 2048, 1024, 2, 3),
-                                             (33, 640, 64, 8, 2), (16, 4096, 256, 5, 4)])
+                                             (33, 640, 64, 8, 2), (16, 4096, 256, 5, 4),
+                                             # groups wider than 1024: the CTA-per-group kernel (-1 = one group per row)
+                                             (6, 4096, -1, 3, 5), (5, 6144, 2048, 4, 3), (3, 12288, -1, 2, 2), (4, 2080, -1, 1, 0)])
 def test_device_quantiser_matches_oracle(N, K, g, q, rounds):
     import lutgemm_b200 as L
     rng = np.random.default_rng(N + K + q)
