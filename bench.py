@@ -411,8 +411,9 @@ def run_quantize(a):
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / a.steps
     weights = a.n * a.k
+    g_eff = a.g if a.g > 0 else a.k                       # --g -1: one group per row, the reference's default
     # bytes that have to move: fp32 weights in, packed planes + fp16 scales out
-    alg_bytes = 4 * weights + weights * a.q // 8 + 2 * (a.k // a.g) * a.q * a.n
+    alg_bytes = 4 * weights + weights * a.q // 8 + 2 * (a.k // g_eff) * a.q * a.n
     line = {"metric": "bcq_quantize_throughput", "value": weights / ms / 1e3, "unit": "Mweights/s", "n_gpus": 1,
             "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
