@@ -250,6 +250,10 @@ int lutgemm_set_gemv_variant(int variant);
  * while no matvec is in flight.  (The reference's half2 atomicAdd accumulation,
  * lutGEMM/src/cuda/kernels/mv_fp16.hpp:95, has no ordered mode.) */
 int lutgemm_set_ordered_reduction(int enabled);
+/* 1 (default): rows that go through the LUT matvec (m = 2, 3; any m with lutgemm_set_batched_path(0)) are taken
+ * two at a time by a two-table kernel that reads the weights once for both; 0: one row per launch.  The pair
+ * kernel is used only with the default reductions (not in ordered mode) and the default matvec variant. */
+int lutgemm_set_row_pairs(int enabled);
 /* 1 (default): m >= 4 runs the tensor-core (tcgen05) kernel, 128 rows per launch, smaller batches one LUT
  * matvec per row; 0: always one LUT matvec per row; 2: tensor-core kernel from m = 2.  All compute the same
  * function. */

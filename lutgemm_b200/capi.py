@@ -22,7 +22,7 @@ SYMBOLS = (
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
     "lutgemm_bcq_quantize", "lutgemm_bcq_quantize_device", "lutgemm_matmul_gptq",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
-    "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_ordered_reduction", "lutgemm_weight_device_status",
+    "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_ordered_reduction", "lutgemm_set_row_pairs", "lutgemm_weight_device_status",
 )
 
 
@@ -99,6 +99,7 @@ def lib():
     L.lutgemm_set_dependent_launch.argtypes = [ip]
     L.lutgemm_set_batched_path.argtypes = [ip]
     L.lutgemm_set_ordered_reduction.argtypes = [ip]
+    L.lutgemm_set_row_pairs.argtypes = [ip]
     L.lutgemm_weight_device_status.argtypes = [vp, C.POINTER(ip)]
     for name in SYMBOLS:
         fn = getattr(L, name)

@@ -16,6 +16,7 @@
 #include "aux_kernels.cuh"
 #include "gemv_tma.cuh"
 #include "gemv_reg.cuh"
+#include "gemv_tma2.cuh"
 #include "gemm_tc.cuh"
 #include "bcq_quantize.cuh"
 #include "gptq3.cuh"
@@ -30,6 +31,7 @@ struct lutgemm_weight {
     int device = 0;
     // split-k workspace: partial sums [ceil(K/512)][N] fp32 and per-tile arrival counters
     float* partial = nullptr;
+    float* partial2 = nullptr;   // second zeroed reduction row [N] of the two-row matvec
     unsigned* counters = nullptr;
     int* status = nullptr;     // device word set by a kernel whose bounded wait ran out
     // TMA descriptors of the packed planes and of alpha (valid when tma_ok)
@@ -57,6 +59,7 @@ std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_ntile_override{0};
 std::atomic<int> g_pdl{1};
 std::atomic<int> g_ordered{0};
+std::atomic<int> g_pairs{1};     // 1: rows that go through the LUT matvec are taken two at a time where possible
 std::atomic<int> g_batched{1};   // 0: one matvec per row; 1: tensor-core kernel from kBatchedFromRows rows; 2: from 2 rows
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
@@ -175,6 +178,8 @@ int alloc_workspace(lutgemm_weight* w) {
     const size_t nslabs = (size_t)(w->K + lg::kSlab2 - 1) / lg::kSlab2;
     LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
     LG_CUDA(cudaMemset(w->partial, 0, nslabs * (size_t)w->N * sizeof(float)));   // row 0 doubles as the reduction row
+    LG_CUDA(cudaMalloc(&w->partial2, (size_t)w->N * sizeof(float)));
+    LG_CUDA(cudaMemset(w->partial2, 0, (size_t)w->N * sizeof(float)));
     LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
     LG_CUDA(cudaMalloc(&w->status, sizeof(int)));
@@ -301,6 +306,56 @@ int launch_gemv_tma_any(const lutgemm_weight* w, const __half* x, __half* y16, f
     const bool bias2 = w->q_bias != nullptr;
     if (w->g % 128 == 0) return launch_gemv_tma<2>(w, p2, grid2, bias2, st);
     return launch_gemv_tma<1>(w, p2, grid2, bias2, st);
+}
+
+template <int WPG>
+int launch_gemv_tma2(const lutgemm_weight* w, const lg::Gemv22Params& p, dim3 grid, bool bias, cudaStream_t st) {
+    static bool configured[64][2] = {};   // the attribute is per device
+    auto kern = bias ? lg::gemv_tma2_kernel<WPG, true> : lg::gemv_tma2_kernel<WPG, false>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev][bias]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kSmemLimit));
+        if (dev < 64) configured[dev][bias] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(lg::kGemv2Threads);
+    cfg.dynamicSmemBytes = (size_t)lg::gemv22_smem_bytes(p.b.a_rows);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    LG_CUDA(cudaLaunchKernelEx(&cfg, kern, w->tmW, w->tmA, p));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+// Two matvec rows in one pass over the weights (rows r and r + 1 of x / y); the caller has checked gemv_pair_ok().
+int gemv_pair(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
+    lg::Gemv22Params p = {};
+    lg::Gemv2Params& b = p.b;
+    b.bW = w->bW; b.alpha = w->alpha; b.q_bias = w->q_bias; b.x = x;
+    b.partial = w->partial; b.counters = w->counters; b.status = w->status; b.y16 = y16; b.y32 = y32;
+    b.N = w->N; b.K = w->K; b.q = w->q; b.g = w->g;
+    int tiles = 0;
+    gemv_tma_geometry(w, &b.nslabs, &b.n_tile, &tiles);
+    b.a_rows = w->a_rows;
+    p.x1 = x + w->K;
+    p.y16_1 = y16 ? y16 + w->N : nullptr;
+    p.y32_1 = y32 ? y32 + w->N : nullptr;
+    p.partial1 = w->partial2;
+    dim3 grid(tiles, b.nslabs);
+    const bool bias = w->q_bias != nullptr;
+    if (w->g % 128 == 0) return launch_gemv_tma2<2>(w, p, grid, bias, st);
+    return launch_gemv_tma2<1>(w, p, grid, bias, st);
+}
+bool gemv_pair_ok(const lutgemm_weight* w) {
+    return g_variant.load() == 0 && w->tma_ok && w->partial2 && !g_ordered.load() && g_pairs.load() &&
+           lg::gemv22_num_stages(w->a_rows) >= 2;
 }
 
 // One matvec row: y (fp16 and/or fp32) = x . W
@@ -452,10 +507,15 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     // m x 17.6 us against 64 us).
     const int batched_mode = g_batched.load();
     if (m == 1 || batched_mode == 0 || (batched_mode == 1 && m < kBatchedFromRows) || !w->tc_ok) {
-        for (int r = 0; r < m; r++) {
-            int rc = gemv_row(w, x + (size_t)r * w->K, y16 ? y16 + (size_t)r * w->N : nullptr,
-                              y32 ? y32 + (size_t)r * w->N : nullptr, st);
+        const bool pairs = gemv_pair_ok(w);
+        for (int r = 0; r < m;) {
+            const int take = (pairs && r + 2 <= m) ? 2 : 1;
+            const __half* xr = x + (size_t)r * w->K;
+            __half* y16r = y16 ? y16 + (size_t)r * w->N : nullptr;
+            float* y32r = y32 ? y32 + (size_t)r * w->N : nullptr;
+            int rc = take == 2 ? gemv_pair(w, xr, y16r, y32r, st) : gemv_row(w, xr, y16r, y32r, st);
             if (rc != LUTGEMM_OK) return rc;
+            r += take;
         }
         return LUTGEMM_OK;
     }
@@ -561,6 +621,7 @@ int lutgemm_weight_destroy(lutgemm_weight_t w) {
         if (w->q_bias) cudaFree(w->q_bias);
     }
     if (w->partial) cudaFree(w->partial);
+    if (w->partial2) cudaFree(w->partial2);
     if (w->counters) cudaFree(w->counters);
     if (w->status) cudaFree(w->status);
     if (w->tc_partial) cudaFree(w->tc_partial);
@@ -981,6 +1042,10 @@ int lutgemm_set_gemv_variant(int variant) {
 
 int lutgemm_set_ordered_reduction(int enabled) {
     g_ordered.store(enabled ? 1 : 0);
+    return LUTGEMM_OK;
+}
+int lutgemm_set_row_pairs(int enabled) {
+    g_pairs.store(enabled ? 1 : 0);
     return LUTGEMM_OK;
 }
 

@@ -345,3 +345,28 @@ def test_random_configurations(seed):
     what = f"N={N} K={K} q={q} g={g} m={m} bias={bias}"
     check(y32, ref, K, what + " fp32 out", fp32_out=True)
     check(y16.astype(np.float32), ref, K, what)
+
+
+@pytest.mark.parametrize("N,K,q,g,m,bias", [(2048, 4096, 3, 128, 2, False), (1032, 1184, 4, 32, 3, True), (512, 512, 1, 512, 2, True),
+                                            (12288, 12288, 3, 128, 2, False), (264, 1536, 8, 64, 3, False), (4096, 3072, 2, 1024, 2, True)])
+def test_two_row_matvec_matches_single_rows(N, K, q, g, m, bias):
+    """m = 2, 3 through the two-table kernel (weights read once for two rows) against the fp32 host reference and against
+    one launch per row."""
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=N + K + m, with_bias=bias, signed_alpha=True,
+                                    alpha_std=min(0.02, 0.6 / np.sqrt(K * q)))
+    x = synth.activations(m, K, seed=m + 40)
+    ref = oracle_y(bW, alpha, qb, g, x)
+    lib = capi.lib()
+    lib.lutgemm_set_batched_path(0)                  # keep the rows on the LUT matvec
+    try:
+        y_pair = run_matmul(bW, alpha, qb, g, x, f32=True)
+        y_pair16 = run_matmul(bW, alpha, qb, g, x)
+        lib.lutgemm_set_row_pairs(0)
+        y_single = run_matmul(bW, alpha, qb, g, x, f32=True)
+    finally:
+        lib.lutgemm_set_row_pairs(1)
+        lib.lutgemm_set_batched_path(1)
+    check(y_pair, ref, K, "two-row kernel, fp32 out", fp32_out=True)
+    check(y_pair16.astype(np.float32), ref, K, "two-row kernel")
+    rms = np.sqrt((ref ** 2).mean())
+    assert np.abs(y_pair - y_single).max() <= 1e-5 * max(rms, 1e-6) * np.sqrt(K / 512)      # same sums, reduction order aside
