@@ -169,6 +169,68 @@ int lutgemm_ipc_open(const void* handle64, void** dptr);
 int lutgemm_ipc_close(void* dptr);
 int lutgemm_ipc_free(void* dptr);
 
+/* ---- A sequence of matvecs in one persistent kernel (no counterpart in the reference, which launches a memset
+ * and a kernel per matvec, lutGEMM/src/kernels.cu:64-71, and has no multi-GPU code). ----
+ *
+ * A decode step of a decoder stack is a fixed list of m = 1 matvecs, most of which consume what an earlier one
+ * produced.  lutgemm_sequence_run executes the whole list in ONE kernel launch: one CTA per SM stays resident,
+ * the weight stream runs across matvec boundaries, and results travel between matvecs (and between the GPUs of a
+ * tensor-parallel group, one process per GPU) in exchange memory whose every 16-byte line carries the step number,
+ * so that a consumer waits on exactly the words it needs and no flag, fence or collective kernel is involved.
+ *
+ * Exchange buffers (lutgemm_seq_buffer; owned by the sequence, identical on every rank):
+ *   kind 1  an fp16 vector of n values, filled by matvecs with out_kind 1 (each rank writes its columns into
+ *           EVERY rank's copy: an all-gather);
+ *   kind 2  `world` fp32 rows of n values, row r filled by rank r's matvec with out_kind 2 on every rank's
+ *           copy; a consumer adds the rows in rank order and rounds to fp16 once (an all-reduce).
+ * Matvec i (lutgemm_seq_op):
+ *   w         the container (a shape the TMA-fed matvec kernel takes; all containers of one sequence have the same
+ *             group size and agree on having q_bias); NULL = no matvec: the `n` values at in_off of a kind-2
+ *             buffer are added, rounded and written to y_ext (the usual last step after a row-parallel matvec)
+ *   in_kind   0: x_ext, an fp16 device vector that is complete when the sequence is launched;
+ *             1 / 2: K values starting at element in_off of buffer in_buf (kind 1 / kind 2)
+ *   out_kind  0: y_ext, an fp16 device vector of N values; 1: N values at element out_off of buffer out_buf;
+ *             2: N values at element out_off of this rank's row of buffer out_buf
+ *   in_off and out_off are multiples of 4.
+ * Pointers are fixed at creation, so a captured launch can be replayed.  Within a step every buffer region is
+ * written once and must be consumed by a later matvec of the same step; all ranks of a group run the same
+ * list the same number of times (the step number is the handshake), and the last matvecs of the list must depend,
+ * directly or not, on every rank (as a row-parallel matvec followed by the NULL step does), so that no rank can
+ * run a step ahead of a reader.
+ *
+ * Set-up with world > 1: every rank creates its sequence, exports the 64-byte handle of its exchange memory,
+ * passes it to the other ranks by any host channel, connects theirs, then commits.  world == 1 needs only create.
+ * lutgemm_sequence_run is asynchronous on `stream`, allocates nothing and synchronises nothing.  Every in-kernel
+ * wait is bounded (lutgemm_sequence_set_wait_limit, 2 s by default): when a producer never shows up the kernel
+ * records a status (lutgemm_sequence_status: 4 = a peer's data did not arrive, 1 / 2 = weight stream), stops waiting
+ * and ends; results of that step are then invalid. */
+typedef struct lutgemm_sequence* lutgemm_sequence_t;
+typedef struct lutgemm_seq_buffer {
+    int kind;            /* 1: fp16 vector; 2: `world` fp32 rows */
+    int n;               /* values (per row); a multiple of 4 */
+} lutgemm_seq_buffer;
+typedef struct lutgemm_seq_op {
+    lutgemm_weight_t w;
+    int in_kind, in_buf, in_off;
+    int out_kind, out_buf, out_off;
+    int n;               /* w == NULL only: how many values to add and write */
+    const void* x_ext;   /* in_kind 0 */
+    void* y_ext;         /* out_kind 0 */
+} lutgemm_seq_op;
+int lutgemm_sequence_create(lutgemm_sequence_t* out, const lutgemm_seq_op* ops, int n_ops,
+                            const lutgemm_seq_buffer* buffers, int n_buffers, int rank, int world);
+int lutgemm_sequence_export(lutgemm_sequence_t s, void* handle64);
+int lutgemm_sequence_connect(lutgemm_sequence_t s, int peer_rank, const void* handle64);
+int lutgemm_sequence_commit(lutgemm_sequence_t s);
+int lutgemm_sequence_run(lutgemm_sequence_t s, void* stream);
+/* Synchronises with the device and reads the sequence's status word (0 = every wait was met). */
+int lutgemm_sequence_status(lutgemm_sequence_t s, int* status);
+/* Time limit of one in-kernel wait for another matvec's or rank's data, in milliseconds (default 2000). */
+int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds);
+/* Kernel launches one lutgemm_sequence_run makes (1) and the CTAs it uses; for reports. */
+int lutgemm_sequence_describe(lutgemm_sequence_t s, int* launches_per_run, int* ctas, size_t* exchange_bytes);
+int lutgemm_sequence_destroy(lutgemm_sequence_t s);
+
 /* Dense fp16 weight on the device: W[k][N] (column-wise) or W[n][K] (row-wise),
  * W = sum_b +-alpha, fp32 sum over planes b = 0..q-1 and one fp16 rounding, no q_bias.
  * Replaces lutGEMM::dequantize_gpu (lutGEMM/src/nQWeight_fp16.cu:29-35) and is bit-identical to

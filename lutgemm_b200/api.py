@@ -260,3 +260,76 @@ def matmul_gptq(m, n, k, scale, bias, A, B, C, stream=None):
 
 
 matmul_gptq_faster = matmul_gptq
+
+
+class MatvecSequence:
+    """A fixed list of m = 1 matvecs executed by ONE persistent kernel launch (lutgemm_sequence_* in the C ABI).
+
+    ops: dicts with keys  w (nQWeight_fp16 or None), in_kind / in_buf / in_off, out_kind / out_buf / out_off, n,
+         x_ext / y_ext (fp16 CUDA tensors; kept alive by this object).  Missing keys are 0 / None.
+    buffers: (kind, n) pairs: kind 1 = fp16 vector of n values, kind 2 = `world` fp32 rows of n values.
+    With world > 1 the ranks' exchange-memory handles are swapped through torch.distributed (default group).
+    """
+
+    def __init__(self, ops, buffers=(), rank=0, world=1):
+        lib = capi.lib()
+        self._keep = []
+        arr = (capi.SeqOp * len(ops))()
+        for i, o in enumerate(ops):
+            w = o.get("w")
+            arr[i].w = w.handle if w is not None else None
+            for k in ("in_kind", "in_buf", "in_off", "out_kind", "out_buf", "out_off", "n"):
+                setattr(arr[i], k, int(o.get(k, 0)))
+            for k in ("x_ext", "y_ext"):
+                t = o.get(k)
+                if t is not None:
+                    self._keep.append(t)
+                    setattr(arr[i], k, t.data_ptr())
+            self._keep.append(w)
+        barr = (capi.SeqBuffer * max(1, len(buffers)))()
+        for i, (kind, n) in enumerate(buffers):
+            barr[i].kind, barr[i].n = int(kind), int(n)
+        self._h = C.c_void_p()
+        self.rank, self.world = rank, world
+        capi.check(lib.lutgemm_sequence_create(C.byref(self._h), arr, len(ops), barr, len(buffers), rank, world),
+                   "sequence_create")
+        if world > 1:
+            import torch.distributed as dist
+            mine = (C.c_ubyte * 64)()
+            capi.check(lib.lutgemm_sequence_export(self._h, mine), "sequence_export")
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(mine))
+            for r in range(world):
+                if r != rank:
+                    hb = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+                    capi.check(lib.lutgemm_sequence_connect(self._h, r, hb), "sequence_connect")
+            capi.check(lib.lutgemm_sequence_commit(self._h), "sequence_commit")
+            dist.barrier()
+
+    def run(self, stream=None):
+        capi.check(capi.lib().lutgemm_sequence_run(self._h, _stream_ptr(stream)), "sequence_run")
+
+    def status(self):
+        st = C.c_int(-1)
+        capi.check(capi.lib().lutgemm_sequence_status(self._h, C.byref(st)), "sequence_status")
+        return st.value
+
+    def set_wait_limit(self, milliseconds):
+        capi.check(capi.lib().lutgemm_sequence_set_wait_limit(self._h, int(milliseconds)), "sequence_set_wait_limit")
+
+    def describe(self):
+        a, b, c = C.c_int(), C.c_int(), C.c_size_t()
+        capi.check(capi.lib().lutgemm_sequence_describe(self._h, C.byref(a), C.byref(b), C.byref(c)), "sequence_describe")
+        return {"launches_per_run": a.value, "ctas": b.value, "exchange_bytes": c.value}
+
+    def close(self):
+        if self._h:
+            capi.lib().lutgemm_sequence_destroy(self._h)
+            self._h = C.c_void_p()
+            self._keep = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

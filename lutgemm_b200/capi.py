@@ -17,6 +17,9 @@ SYMBOLS = (
     "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
     "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matvec_static_scratch", "lutgemm_dequantize",
     "lutgemm_matvec_tp", "lutgemm_matvec_tiles", "lutgemm_tp_finalize",
+    "lutgemm_sequence_create", "lutgemm_sequence_export", "lutgemm_sequence_connect", "lutgemm_sequence_commit",
+    "lutgemm_sequence_run", "lutgemm_sequence_status", "lutgemm_sequence_set_wait_limit", "lutgemm_sequence_describe",
+    "lutgemm_sequence_destroy",
     "lutgemm_ipc_alloc", "lutgemm_ipc_open", "lutgemm_ipc_close", "lutgemm_ipc_free",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
@@ -37,6 +40,16 @@ class TpLink(C.Structure):
                 ("x_slots", C.c_void_p), ("x_slot_stride", C.c_int), ("x_off", C.c_int),
                 ("flag_in", C.c_void_p), ("flag_target", C.c_uint), ("done_counter", C.c_void_p),
                 ("out16", C.c_void_p * 8), ("out32", C.c_void_p * 8), ("flag_out", C.c_void_p * 8)]
+
+
+class SeqBuffer(C.Structure):
+    _fields_ = [("kind", C.c_int), ("n", C.c_int)]
+
+
+class SeqOp(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("in_kind", C.c_int), ("in_buf", C.c_int), ("in_off", C.c_int),
+                ("out_kind", C.c_int), ("out_buf", C.c_int), ("out_off", C.c_int), ("n", C.c_int),
+                ("x_ext", C.c_void_p), ("y_ext", C.c_void_p)]
 
 
 class LutGemmError(RuntimeError):
@@ -76,6 +89,15 @@ def lib():
     L.lutgemm_matvec_tp.argtypes = [vp, vp, C.POINTER(TpLink), vp, vp, vp]
     L.lutgemm_matvec_tiles.argtypes = [vp, C.POINTER(ip)]
     L.lutgemm_tp_finalize.argtypes = [vp, vp, vp, ip, ip, ip, vp, C.c_uint, vp, vp]
+    L.lutgemm_sequence_create.argtypes = [C.POINTER(vp), C.POINTER(SeqOp), ip, C.POINTER(SeqBuffer), ip, ip, ip]
+    L.lutgemm_sequence_export.argtypes = [vp, vp]
+    L.lutgemm_sequence_connect.argtypes = [vp, ip, vp]
+    L.lutgemm_sequence_commit.argtypes = [vp]
+    L.lutgemm_sequence_run.argtypes = [vp, vp]
+    L.lutgemm_sequence_status.argtypes = [vp, C.POINTER(ip)]
+    L.lutgemm_sequence_set_wait_limit.argtypes = [vp, ip]
+    L.lutgemm_sequence_describe.argtypes = [vp, C.POINTER(ip), C.POINTER(ip), C.POINTER(C.c_size_t)]
+    L.lutgemm_sequence_destroy.argtypes = [vp]
     L.lutgemm_ipc_alloc.argtypes = [C.c_size_t, C.POINTER(vp), vp]
     L.lutgemm_ipc_open.argtypes = [vp, C.POINTER(vp)]
     L.lutgemm_ipc_close.argtypes = [vp]

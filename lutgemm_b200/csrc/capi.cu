@@ -17,6 +17,7 @@
 #include "gemv_tma.cuh"
 #include "gemv_reg.cuh"
 #include "gemv_tma2.cuh"
+#include "gemv_seq.cuh"
 #include "gemm_tc.cuh"
 #include "bcq_quantize.cuh"
 #include "gptq3.cuh"
@@ -50,6 +51,25 @@ struct lutgemm_weight {
     void* d_stage_in = nullptr;
     void* d_stage_out = nullptr;
     size_t stage_rows = 0;
+};
+
+struct lutgemm_sequence {
+    int rank = 0, world = 1, device = 0;
+    std::vector<lutgemm_seq_op> ops;
+    std::vector<lutgemm_seq_buffer> bufs;
+    std::vector<size_t> buf_off;           // byte offset of every buffer inside the exchange memory
+    size_t xchg_bytes = 0;
+    unsigned char* xchg[8] = {};           // [rank] = this GPU's exchange memory, others: peer mappings
+    bool mapped[8] = {};
+    std::vector<lg::SeqOpDev> h_ops;
+    lg::SeqOpDev* d_ops = nullptr;
+    lg::SeqParams* params = nullptr;       // the kernel's parameter block (host copy; holds every matvec's geometry)
+    float* partial = nullptr;              // one zeroed fp32 row per matvec, back to back
+    unsigned* counters = nullptr;          // arrival counters per column tile, back to back
+    unsigned* words = nullptr;             // [0] step number, [1] finished CTAs, [2] status
+    int a_rows = 1, wpg = 2, grid = 0;
+    bool bias = false, committed = false;
+    unsigned long long wait_ns = 2000000000ull;
 };
 
 namespace {
@@ -539,6 +559,33 @@ int finish_create(lutgemm_weight* w, lutgemm_weight_t* out) {
     return LUTGEMM_OK;
 }
 
+size_t seq_buffer_bytes(const lutgemm_seq_buffer& b, int world) {
+    // one 16-byte line per 4 fp16 values / per 2 fp32 values
+    const size_t raw = b.kind == 1 ? (size_t)b.n * 4 : (size_t)world * b.n * 8;
+    return (raw + 255) / 256 * 256;
+}
+
+template <int WPG, bool BIAS>
+int launch_sequence(lutgemm_sequence* s, cudaStream_t st) {
+    static bool configured[64] = {};
+    auto kern = lg::gemv_seq_kernel<WPG, BIAS>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kSmemLimit));
+        if (dev < 64) configured[dev] = true;
+    }
+    lg::SeqParams& p = *s->params;
+    p.wait_ns = s->wait_ns;
+    // cooperative launch: the runtime guarantees that all CTAs are resident together (they wait on one another),
+    // or refuses the launch
+    void* args[] = {&p};
+    LG_CUDA(cudaLaunchCooperativeKernel((void*)kern, dim3(s->grid), dim3(lg::kSeqThreads), args,
+                                        (size_t)lg::seq_smem_bytes(s->a_rows), st));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return LUTGEMM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -790,6 +837,202 @@ int lutgemm_ipc_close(void* dptr) {
 int lutgemm_ipc_free(void* dptr) {
     if (!dptr) return LUTGEMM_OK;
     LG_CUDA(cudaFree(dptr));
+    return LUTGEMM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// sequences of matvecs in one persistent kernel (gemv_seq.cuh)
+int lutgemm_sequence_create(lutgemm_sequence_t* out, const lutgemm_seq_op* ops, int n_ops,
+                            const lutgemm_seq_buffer* buffers, int n_buffers, int rank, int world) {
+    if (!out || !ops || (n_buffers > 0 && !buffers)) return LUTGEMM_ERR_NULL;
+    if (n_ops < 1 || n_buffers < 0 || world < 1 || world > 8 || rank < 0 || rank >= world) return LUTGEMM_ERR_SHAPE;
+    if (n_ops > lg::kSeqMaxOps) return LUTGEMM_ERR_TOO_LARGE;
+    for (int b = 0; b < n_buffers; b++)
+        if ((buffers[b].kind != 1 && buffers[b].kind != 2) || buffers[b].n < 4 || buffers[b].n % 4 != 0) return LUTGEMM_ERR_SHAPE;
+    const lutgemm_weight* first = nullptr;
+    for (int i = 0; i < n_ops; i++) {
+        const lutgemm_seq_op& o = ops[i];
+        if (o.in_kind < 0 || o.in_kind > 2 || o.out_kind < 0 || o.out_kind > 2) return LUTGEMM_ERR_SHAPE;
+        const int K = o.w ? o.w->K : o.n, N = o.w ? o.w->N : o.n;
+        if (!o.w && (o.in_kind != 2 || o.out_kind != 0 || o.n < 4 || o.n % 4 != 0)) return LUTGEMM_ERR_SHAPE;
+        if (o.in_kind == 0) {
+            if (!o.x_ext) return LUTGEMM_ERR_NULL;
+            if ((uintptr_t)o.x_ext & 15) return LUTGEMM_ERR_ALIGN;
+        } else {
+            if (o.in_buf < 0 || o.in_buf >= n_buffers || buffers[o.in_buf].kind != o.in_kind) return LUTGEMM_ERR_SHAPE;
+            if (o.in_off < 0 || o.in_off % 4 != 0 || o.in_off + K > buffers[o.in_buf].n) return LUTGEMM_ERR_SHAPE;
+        }
+        if (o.out_kind == 0) {
+            if (!o.y_ext) return LUTGEMM_ERR_NULL;
+            if ((uintptr_t)o.y_ext & 15) return LUTGEMM_ERR_ALIGN;
+        } else {
+            if (o.out_buf < 0 || o.out_buf >= n_buffers || buffers[o.out_buf].kind != o.out_kind) return LUTGEMM_ERR_SHAPE;
+            if (o.out_off < 0 || o.out_off % 4 != 0 || o.out_off + N > buffers[o.out_buf].n) return LUTGEMM_ERR_SHAPE;
+        }
+        if (o.w) {
+            if (!o.w->tma_ok) return LUTGEMM_ERR_SHAPE;
+            if (!first) first = o.w;
+            if (o.w->a_rows != first->a_rows || (o.w->g % 128 == 0) != (first->g % 128 == 0) ||
+                (o.w->q_bias != nullptr) != (first->q_bias != nullptr))
+                return LUTGEMM_ERR_SHAPE;
+        }
+    }
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    lutgemm_sequence* s = new (std::nothrow) lutgemm_sequence();
+    if (!s) return LUTGEMM_ERR_TOO_LARGE;
+    s->rank = rank; s->world = world; s->device = dev;
+    s->ops.assign(ops, ops + n_ops);
+    if (n_buffers) s->bufs.assign(buffers, buffers + n_buffers);
+    if (first) { s->a_rows = first->a_rows; s->wpg = first->g % 128 == 0 ? 2 : 1; s->bias = first->q_bias != nullptr; }
+    size_t off = 0;
+    for (int b = 0; b < n_buffers; b++) { s->buf_off.push_back(off); off += seq_buffer_bytes(buffers[b], world); }
+    s->xchg_bytes = off ? off : 256;
+#define LG_SEQ_TRY(call) do { cudaError_t e__ = (call); if (e__ != cudaSuccess) { g_last_cuda = (int)e__; lutgemm_sequence_destroy(s); \
+        return (e__ == cudaErrorNoDevice || e__ == cudaErrorInsufficientDriver) ? LUTGEMM_ERR_NO_DEVICE : LUTGEMM_ERR_CUDA; } } while (0)
+    LG_SEQ_TRY(cudaMalloc(&s->xchg[rank], s->xchg_bytes));
+    LG_SEQ_TRY(cudaMemset(s->xchg[rank], 0, s->xchg_bytes));           // step numbers start at 1: nothing is valid yet
+    s->mapped[rank] = true;
+    // geometry and workspace of every matvec
+    s->h_ops.resize(n_ops);
+    size_t n_partial = 0, n_counters = 0;
+    s->grid = sm_count();
+    for (int i = 0; i < n_ops; i++) {
+        lg::SeqOpDev& d = s->h_ops[i];
+        std::memset(&d, 0, sizeof(d));
+        const lutgemm_seq_op& o = ops[i];
+        if (!o.w) {
+            d.reduce_only = 1; d.N = d.K = o.n; d.items = (o.n + lg::kSlab2 - 1) / lg::kSlab2;
+        } else {
+            d.tmW = o.w->tmW; d.tmA = o.w->tmA; d.q_bias = o.w->q_bias;
+            d.N = o.w->N; d.K = o.w->K; d.q = o.w->q; d.g = o.w->g;
+            gemv_tma_geometry(o.w, &d.nslabs, &d.n_tile, &d.tiles);
+            d.items = d.tiles * d.nslabs;
+            n_partial += ((size_t)d.N + 63) / 64 * 64;
+            n_counters += (size_t)d.tiles;
+        }
+        d.in_kind = o.in_kind; d.out_kind = o.out_kind; d.out_world = world;
+        d.in_rows = world;
+        if (o.in_kind == 2) d.in_row_lines = s->bufs[o.in_buf].n / 2;
+    }
+    LG_SEQ_TRY(cudaMalloc(&s->partial, (n_partial + 64) * sizeof(float)));
+    LG_SEQ_TRY(cudaMemset(s->partial, 0, (n_partial + 64) * sizeof(float)));
+    LG_SEQ_TRY(cudaMalloc(&s->counters, (n_counters + 64) * sizeof(unsigned)));
+    LG_SEQ_TRY(cudaMemset(s->counters, 0, (n_counters + 64) * sizeof(unsigned)));
+    LG_SEQ_TRY(cudaMalloc(&s->words, 64));
+    {
+        const unsigned init[4] = {1u, 0u, 0u, 0u};
+        LG_SEQ_TRY(cudaMemcpy(s->words, init, sizeof(init), cudaMemcpyHostToDevice));
+    }
+    LG_SEQ_TRY(cudaMalloc(&s->d_ops, (size_t)n_ops * sizeof(lg::SeqOpDev)));
+    size_t po = 0, co = 0;
+    for (int i = 0; i < n_ops; i++) {
+        lg::SeqOpDev& d = s->h_ops[i];
+        if (d.reduce_only) continue;
+        d.partial = s->partial + po; po += ((size_t)d.N + 63) / 64 * 64;
+        d.counters = s->counters + co; co += (size_t)d.tiles;
+    }
+#undef LG_SEQ_TRY
+    *out = s;
+    if (world == 1) return lutgemm_sequence_commit(s);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_export(lutgemm_sequence_t s, void* handle64) {
+    if (!s || !handle64) return LUTGEMM_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    LG_CUDA(cudaIpcGetMemHandle(&h, s->xchg[s->rank]));
+    std::memcpy(handle64, &h, 64);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_connect(lutgemm_sequence_t s, int peer_rank, const void* handle64) {
+    if (!s || !handle64) return LUTGEMM_ERR_NULL;
+    if (peer_rank < 0 || peer_rank >= s->world || peer_rank == s->rank || s->mapped[peer_rank]) return LUTGEMM_ERR_SHAPE;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    void* ptr = nullptr;
+    LG_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    s->xchg[peer_rank] = (unsigned char*)ptr;
+    s->mapped[peer_rank] = true;
+    s->committed = false;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_commit(lutgemm_sequence_t s) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    for (int r = 0; r < s->world; r++)
+        if (!s->mapped[r]) return LUTGEMM_ERR_NULL;
+    for (size_t i = 0; i < s->ops.size(); i++) {
+        const lutgemm_seq_op& o = s->ops[i];
+        lg::SeqOpDev& d = s->h_ops[i];
+        if (o.in_kind == 0) d.in_ptr = o.x_ext;
+        else d.in_ptr = s->xchg[s->rank] + s->buf_off[o.in_buf] + (size_t)(o.in_off / (o.in_kind == 1 ? 4 : 2)) * 16;
+        for (int r = 0; r < 8; r++) d.out_ptr[r] = nullptr;
+        if (o.out_kind == 0) d.out_ptr[0] = o.y_ext;
+        else if (o.out_kind == 1)
+            for (int r = 0; r < s->world; r++) d.out_ptr[r] = s->xchg[r] + s->buf_off[o.out_buf] + (size_t)(o.out_off / 4) * 16;
+        else
+            for (int r = 0; r < s->world; r++)
+                d.out_ptr[r] = s->xchg[r] + s->buf_off[o.out_buf] + ((size_t)s->rank * (s->bufs[o.out_buf].n / 2) + o.out_off / 2) * 16;
+    }
+    LG_CUDA(cudaMemcpy(s->d_ops, s->h_ops.data(), s->h_ops.size() * sizeof(lg::SeqOpDev), cudaMemcpyHostToDevice));
+    if (!s->params) s->params = new (std::nothrow) lg::SeqParams();
+    if (!s->params) return LUTGEMM_ERR_TOO_LARGE;
+    lg::SeqParams& p = *s->params;
+    std::memset(&p, 0, sizeof(p));
+    p.ops = s->d_ops; p.n_ops = (int)s->h_ops.size(); p.a_rows = s->a_rows;
+    p.epoch = s->words; p.done = s->words + 1; p.status = (int*)(s->words + 2); p.wait_ns = s->wait_ns;
+    for (size_t i = 0; i < s->h_ops.size(); i++) {
+        const lg::SeqOpDev& d = s->h_ops[i];
+        p.geo[i] = lg::SeqGeo{d.N, d.K, d.n_tile, d.tiles, d.nslabs, d.q, d.g, d.reduce_only};
+    }
+    s->committed = true;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_run(lutgemm_sequence_t s, void* stream) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    if (!s->committed) return LUTGEMM_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (s->wpg == 2) return s->bias ? launch_sequence<2, true>(s, st) : launch_sequence<2, false>(s, st);
+    return s->bias ? launch_sequence<1, true>(s, st) : launch_sequence<1, false>(s, st);
+}
+
+int lutgemm_sequence_status(lutgemm_sequence_t s, int* status) {
+    if (!s || !status) return LUTGEMM_ERR_NULL;
+    LG_CUDA(cudaMemcpy(status, s->words + 2, sizeof(int), cudaMemcpyDeviceToHost));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    if (milliseconds < 1 || milliseconds > 60000) return LUTGEMM_ERR_SHAPE;
+    s->wait_ns = (unsigned long long)milliseconds * 1000000ull;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_describe(lutgemm_sequence_t s, int* launches_per_run, int* ctas, size_t* exchange_bytes) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    if (launches_per_run) *launches_per_run = 1;
+    if (ctas) *ctas = s->grid;
+    if (exchange_bytes) *exchange_bytes = s->xchg_bytes;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_sequence_destroy(lutgemm_sequence_t s) {
+    if (!s) return LUTGEMM_OK;
+    for (int r = 0; r < 8; r++) {
+        if (!s->xchg[r]) continue;
+        if (r == s->rank) cudaFree(s->xchg[r]);
+        else cudaIpcCloseMemHandle(s->xchg[r]);
+    }
+    if (s->partial) cudaFree(s->partial);
+    if (s->counters) cudaFree(s->counters);
+    if (s->words) cudaFree(s->words);
+    if (s->d_ops) cudaFree(s->d_ops);
+    delete s->params;
+    delete s;
     return LUTGEMM_OK;
 }
 

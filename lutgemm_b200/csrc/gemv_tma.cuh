@@ -69,7 +69,7 @@ __host__ __device__ constexpr int gemv2_smem_bytes(int a_rows) {
     return kStage0Off + gemv2_num_stages(a_rows) * gemv2_stage_bytes(a_rows);
 }
 
-enum { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusConsumerTimeout = 2, kStatusPeerTimeout = 4 };
+enum { kStatusOk = 0, kStatusProducerTimeout = 1, kStatusConsumerTimeout = 2, kStatusPeerTimeout = 4, kStatusLayout = 8 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     unsigned v;
@@ -180,31 +180,20 @@ __device__ __forceinline__ float2 lookup_word(const unsigned char* lut, uint32_t
 // Table for the 64 chunks of one slab.  Consumer thread t owns slot (t & 63) and the 32 entries
 // idx in [32 (t >> 6), +32), walked in Gray-code order (one add per entry).  A warp stores 32
 // consecutive slots of one idx row: conflict free.
-__device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, int k0, int K, int ctid, const TpLink& tp) {
-    const int slot = ctid & 63, part = ctid >> 6;
+__device__ __forceinline__ int lut_chunk_of(int ctid) {
+    const int slot = ctid & 63;
     const int u = slot >> 5, G = (slot >> 3) & 3, jp = (slot >> 2) & 1, beta = slot & 3;
-    const int chunk = 4 * (4 * G + jp + 2 * u) + beta;       // 8-activation chunk in natural k order
-    float xv[8];
-    if (tp.x_mode == 2) {
-        // all-reduced input: add the ranks' fp32 rows in rank order, round to fp16 once
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (k0 + 8 * chunk < K) {
-            for (int r = 0; r < tp.world; r++) {
-                const float4* src = reinterpret_cast<const float4*>(tp.x_slots + (size_t)r * tp.x_slot_stride + tp.x_off + k0 + 8 * chunk);
-                const float4 a = __ldcg(src), b = __ldcg(src + 1);
-                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-            }
-        }
-#pragma unroll
-        for (int t = 0; t < 8; t++) xv[t] = __half2float(__float2half_rn(acc[t]));
-    } else {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (k0 + 8 * chunk < K) raw = __ldcg(reinterpret_cast<const uint4*>(x + k0 + 8 * chunk));
-        const float2 f0 = half2_bits_to_float2(raw.x), f1 = half2_bits_to_float2(raw.y);
-        const float2 f2 = half2_bits_to_float2(raw.z), f3 = half2_bits_to_float2(raw.w);
-        xv[0] = f0.x; xv[1] = f0.y; xv[2] = f1.x; xv[3] = f1.y; xv[4] = f2.x; xv[5] = f2.y; xv[6] = f3.x; xv[7] = f3.y;
-    }
+    return 4 * (4 * G + jp + 2 * u) + beta;                   // 8-activation chunk in natural k order
+}
+// The 8 fp16 activations of this thread's chunk (zero beyond K).
+__device__ __forceinline__ uint4 load_x_chunk(const __half* x, int k0, int K, int ctid) {
+    const int chunk = lut_chunk_of(ctid);
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (k0 + 8 * chunk < K) raw = __ldcg(reinterpret_cast<const uint4*>(x + k0 + 8 * chunk));
+    return raw;
+}
+__device__ __forceinline__ void build_lut_from(unsigned char* lut, const float (&xv)[8], int ctid) {
+    const int slot = ctid & 63, part = ctid >> 6;
     float e = -xv[0] - xv[1] - xv[2] - xv[3] - xv[4];
     e += (part & 1) ? xv[5] : -xv[5];
     e += (part & 2) ? xv[6] : -xv[6];
@@ -218,6 +207,35 @@ __device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, 
         const float two_x = 2.0f * xv[t];
         e = ((gcode >> t) & 1) ? e + two_x : e - two_x;
         *reinterpret_cast<float*>(base + gcode * 256) = e;
+    }
+}
+// The same from the chunk's 8 fp16 values as loaded (16 bytes).
+__device__ __forceinline__ void build_lut_from_raw(unsigned char* lut, uint4 raw, int ctid) {
+    float xv[8];
+    const float2 f0 = half2_bits_to_float2(raw.x), f1 = half2_bits_to_float2(raw.y);
+    const float2 f2 = half2_bits_to_float2(raw.z), f3 = half2_bits_to_float2(raw.w);
+    xv[0] = f0.x; xv[1] = f0.y; xv[2] = f1.x; xv[3] = f1.y; xv[4] = f2.x; xv[5] = f2.y; xv[6] = f3.x; xv[7] = f3.y;
+    build_lut_from(lut, xv, ctid);
+}
+__device__ __forceinline__ void build_lut2(unsigned char* lut, const __half* x, int k0, int K, int ctid, const TpLink& tp) {
+    if (tp.x_mode == 2) {
+        // all-reduced input: add the ranks' fp32 rows in rank order, round to fp16 once
+        const int chunk = lut_chunk_of(ctid);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (k0 + 8 * chunk < K) {
+            for (int r = 0; r < tp.world; r++) {
+                const float4* src = reinterpret_cast<const float4*>(tp.x_slots + (size_t)r * tp.x_slot_stride + tp.x_off + k0 + 8 * chunk);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+            }
+        }
+        float xv[8];
+#pragma unroll
+        for (int t = 0; t < 8; t++) xv[t] = __half2float(__float2half_rn(acc[t]));
+        build_lut_from(lut, xv, ctid);
+    } else {
+        build_lut_from_raw(lut, load_x_chunk(x, k0, K, ctid), ctid);
     }
 }
 

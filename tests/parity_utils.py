@@ -20,3 +20,11 @@ MAE = 1e-3          # on the fp16 output for k <= 12288, on the fp32 output for 
 # weight is itself rounded to fp16, a +-2^-12 relative perturbation of every weight; the relative error
 # is then taken with a floor of 0.1 * rms(ref) in the denominator.
 REF16_FLOOR = 0.1
+
+
+def assert_parity(y, ref, K, what=""):
+    """The matvec tolerance: max relative error on the fp16 output, MAE where fp16 rounding allows it."""
+    rel, mae = error_metrics(y, ref)
+    assert rel <= MAX_REL, f"{what}: max rel err {rel:.3e}"
+    if K <= 12288:
+        assert mae <= MAE, f"{what}: MAE {mae:.3e}"

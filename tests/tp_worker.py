@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from lutgemm_b200 import synth, tp_fused, tp_stack  # noqa: E402
+from lutgemm_b200 import synth, tp_fused, tp_seq, tp_stack  # noqa: E402
 
 
 def main():
@@ -18,7 +18,8 @@ def main():
     H, F, Q, G, LAYERS = 1024, 2048, 3, 128, 3
     dev = f"cuda:{local}"
     plain = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, rank=rank, world=world, device=dev, seed=1, generate="host")
-    fused = tp_fused.FusedTPStack(H, F, Q, G, LAYERS, rank=rank, world=world, device=dev, seed=1, generate="host")
+    cls = tp_seq.SeqTPStack if "--seq" in sys.argv else tp_fused.FusedTPStack      # one launch per step / one per matvec
+    fused = cls(H, F, Q, G, LAYERS, rank=rank, world=world, device=dev, seed=1, generate="host")
     x = torch.from_numpy(synth.activations(1, H, seed=4).view(np.int16)).cuda().view(torch.float16).reshape(-1)
     want = plain.step(x).float().cpu().numpy()
     ok = True
