@@ -8,8 +8,11 @@ planes, group size 128, random BCQ weights.  One "step" is one matvec on each of
 sets (ROT x 63.75 MB > 4x the 126 MB L2, so every matvec streams its weights from HBM).
 `value` is effective GB/s = algorithmic bytes / device time with everything resident in HBM;
 `e2e` is the same through the host-buffer C-ABI call (H2D of x and D2H of y inside the timed region).
-With N > 1 ranks every rank runs the same workload on its own weight sets (independent layers, no
-collective on the data path: weak scaling); time is the max over ranks.
+With N > 1 ranks (one process per GPU) the workload is the tensor-parallel decoder linear stack (96 layers x
+{QKV, out-proj, FC1, FC2}, hidden 12288, FFN 49152, q = 3, g = 128, m = 1; column-parallel + all-gather,
+row-parallel + all-reduce): strong scaling, value = the stack's algorithmic bytes / step time, max over ranks.
+A step is one kernel launch per GPU (lutgemm_sequence_run).  The N = 1 line carries the same stack on one GPU under
+"stack_tp1", so that the N-GPU numbers can be divided by a one-GPU number of the same workload.
 
 `--impl reference` times the reference's CPU path for the same matvec on the host cores:
 lutGEMM::dequantize_cpu (compiled from the reference sources into oracle/_ref, run on k-slabs by
@@ -56,8 +59,10 @@ def parse():
                          "quantize: the BCQ quantiser (greedy + --rounds refinements) on an [n, k] fp32 layer, a side line; "
                          "gptq: the 3-bit uniform comparison matvec (matmul_gptq), with the reference's two kernels beside it")
     ap.add_argument("--rounds", type=int, default=15, help="quantize workload: refinement rounds")
-    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
-                    help="stack workload: exchange steps fused into the matvec kernels (peer pushes) or NCCL collectives")
+    ap.add_argument("--tp", default="seq", choices=["seq", "fused", "nccl"],
+                    help="stack workload: seq = the whole step as one persistent kernel per GPU (exchange lines over NVLink); "
+                         "fused = one kernel per matvec with the exchange fused in (peer pushes + flags); nccl = NCCL collectives")
+    ap.add_argument("--no-stack-tp1", action="store_true", help="skip the one-GPU stack anchor of the default run")
     ap.add_argument("--layers", type=int, default=96, help="decoder layers of the stack workload")
     ap.add_argument("--hidden", type=int, default=12288)
     ap.add_argument("--ffn", type=int, default=49152)
@@ -272,57 +277,34 @@ def shutdown_process_group(dist_mod):
         os._exit(0)
 
 
-def run_stack(a):
-    """Tensor-parallel decoder linear stack (BASELINE config 5): `layers` x {QKV, out, FC1, FC2} at m = 1, sharded over
-    the ranks (column-parallel + all-gather, row-parallel + all-reduce).  Strong scaling: the stack is the same at every N.
-    value = algorithmic bytes of the whole stack / step time (max over ranks), i.e. aggregate effective GB/s."""
+def time_stack(a, stack, x, rank, world, dist, barrier, tp):
+    """Warm-up, CUDA-graph capture and the timed loop of one stack object; returns (seconds per step, launch kind, clocks)."""
     import torch
-    import torch.distributed as dist
-    from lutgemm_b200 import capi, tp_stack
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    lib = capi.lib()
-    lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
-    if a.tp == "fused":
-        from lutgemm_b200 import tp_fused
-        stack = tp_fused.FusedTPStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    if tp == "seq":
+        stack.x_in.copy_(x)
+        step = lambda: stack.step()
     else:
-        stack = tp_stack.TPLinearStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
-    B = tp_stack.stack_algorithmic_bytes(a.hidden, a.ffn, a.q, a.g, a.layers)
-    x_host = synth.activations(1, a.hidden, seed=5).reshape(-1)
-    x = torch.from_numpy(x_host.view(np.int16).copy()).cuda().view(torch.float16)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+        step = lambda: stack.step(x)
     for _ in range(max(3, a.warmup)):
-        stack.step(x)
+        step()
     barrier()
-    run_step, graph = (lambda: stack.step(x)), None
+    run_step, graph = step, None
     if not a.no_graph:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                stack.step(x)
+                step()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    stack.step(x)
+                    step()
             torch.cuda.current_stream().wait_stream(side)
             run_step = graph.replay
             for _ in range(2):
                 run_step()
-        except Exception as e:          # capture of the collectives refused: time eager launches instead
-            graph, run_step = None, (lambda: stack.step(x))
+        except Exception as e:          # capture refused: time eager launches instead
+            graph, run_step = None, step
             if rank == 0:
                 print(f"bench.py: CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
         barrier()
@@ -342,16 +324,83 @@ def run_stack(a):
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    sec_per_step = ms / 1e3 / a.steps
+    kind = "python" if graph is None else "cuda graph of one step, replayed"
+    graph = None
+    run_step = None
+    return ms / 1e3 / a.steps, kind, clocks
+
+
+def make_stack(a, tp, rank, world, local):
+    from lutgemm_b200 import tp_stack
+    if tp == "seq":
+        from lutgemm_b200 import tp_seq
+        return tp_seq.SeqTPStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    if tp == "fused":
+        from lutgemm_b200 import tp_fused
+        return tp_fused.FusedTPStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+    return tp_stack.TPLinearStack(a.hidden, a.ffn, a.q, a.g, a.layers, rank=rank, world=world, device=f"cuda:{local}", seed=11)
+
+
+def run_stack(a):
+    """Tensor-parallel decoder linear stack (BASELINE config 5): `layers` x {QKV, out, FC1, FC2} at m = 1, sharded over
+    the ranks (column-parallel + all-gather, row-parallel + all-reduce).  Strong scaling: the stack is the same at every N.
+    value = algorithmic bytes of the whole stack / step time (max over ranks), i.e. aggregate effective GB/s.
+    Before the timed loop one step of the same shards runs through NCCL collectives and is compared with the path that
+    is timed; after it every rank's device status word is read.  Either check failing ends the run with a non-zero code."""
+    import torch
+    import torch.distributed as dist
+    from lutgemm_b200 import capi, tp_stack
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    lib = capi.lib()
+    lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
+    stack = make_stack(a, a.tp, rank, world, local)
+    B = tp_stack.stack_algorithmic_bytes(a.hidden, a.ffn, a.q, a.g, a.layers)
+    x_host = synth.activations(1, a.hidden, seed=5).reshape(-1)
+    x = torch.from_numpy(x_host.view(np.int16).copy()).cuda().view(torch.float16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # the same shards through the process group's collectives (the parent class's step) against the timed path
+    matches, max_rel = None, None
+    if a.tp != "nccl":
+        want = tp_stack.TPLinearStack.step(stack, x).float().clone()
+        got = stack.step(x).float().clone()
+        torch.cuda.synchronize()
+        denom = float(want.abs().max().item()) + 1e-9
+        max_rel = float((got - want).abs().max().item()) / denom
+        # both paths round to fp16 after each of the 4 x layers matvecs and add their k-slabs in no fixed order, so
+        # they drift apart like a random walk: about 1e-3 of the largest output per sqrt(matvec); garbage would be O(1)
+        tol = max(2e-3, 1e-3 * (4 * a.layers) ** 0.5)
+        flag = torch.tensor([1.0 if (max_rel <= tol and bool(torch.isfinite(got).all())) else 0.0], device="cuda")
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        matches = bool(flag.item() > 0.5)
+    sec_per_step, launch_kind, clocks = time_stack(a, stack, x, rank, world, dist if world > 1 else None, barrier, a.tp)
+    status = stack.device_status() if hasattr(stack, "device_status") else 0
+    st = torch.tensor([float(status)], device="cuda")
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    status = int(st.item())
     # end to end: the step's activation vector comes from pinned host memory and its result goes back every step
     xin = torch.from_numpy(x_host.view(np.int16).copy()).pin_memory()
     yout = torch.empty(a.hidden, dtype=torch.int16).pin_memory()
-    xdev = torch.empty(a.hidden, dtype=torch.float16, device="cuda")
+    xdev = stack.x_in if a.tp == "seq" else torch.empty(a.hidden, dtype=torch.float16, device="cuda")
     barrier()
     t0 = time.perf_counter()
     for _ in range(a.steps):
         xdev.view(torch.int16).copy_(xin, non_blocking=True)
-        y = stack.step(xdev)
+        y = stack.step() if a.tp == "seq" else stack.step(xdev)
         yout.copy_(y.view(torch.int16), non_blocking=True)
         torch.cuda.synchronize()
     dt = time.perf_counter() - t0
@@ -359,31 +408,40 @@ def run_stack(a):
         t = torch.tensor([dt], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
+    ok = status == 0 and matches is not False
     if rank == 0:
         peak, peak_kind = measured_peak()
         value = B / sec_per_step / 1e9
         per_gpu = value / world
+        how = {"seq": "the whole step is one persistent kernel per GPU; results travel between matvecs and GPUs in 16-byte exchange "
+                      "lines that carry the step number (plain peer stores over NVLink)",
+               "fused": "one kernel per matvec, exchange fused in (peer stores + flags over NVLink)",
+               "nccl": "NCCL collectives"}[a.tp]
+        launches = {"seq": 1, "fused": a.layers * 4 + 1, "nccl": a.layers * 4}[a.tp]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(3, a.warmup),
             "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"tensor-parallel decoder linear stack, {a.layers} layers, hidden {a.hidden}, ffn {a.ffn}, "
                                    f"q={a.q} g={a.g} m=1", "parallelism": f"tp{world}: QKV/FC1 column-parallel + all-gather, out-proj/FC2 row-parallel + all-reduce; "
-                                   + ("exchange fused into the matvec kernels (peer stores + flags over NVLink)" if a.tp == "fused"
-                                      else "NCCL collectives"), "algorithmic_bytes_per_step": B,
+                                   + how, "algorithmic_bytes_per_step": B,
                        "l2": f"{B / world / 1e9:.1f} GB of packed weights per GPU per step, far larger than L2",
-                       "launch": "python" if graph is None else "cuda graph of one step, replayed"},
+                       "launch": launch_kind},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_source": peak_kind, "traffic": None, "kernel": "gemv_tma_kernel (per GPU average over the step, collectives included)"},
-            "gpu_launches": int(a.steps * (a.layers * 4 + (1 if a.tp == "fused" else 0))),
+                         "peak_source": peak_kind, "traffic": None,
+                         "kernel": ("gemv_seq_kernel" if a.tp == "seq" else "gemv_tma_kernel") + " (per GPU average over the step, exchange included)"},
+            "gpu_launches": int(a.steps * launches),
+            "device_status": status,
+            "matches_nccl": matches, "max_rel_diff_vs_nccl": max_rel,
+            "matches_nccl_tolerance": None if matches is None else max(2e-3, 1e-3 * (4 * a.layers) ** 0.5),
             "clocks": clocks,
             "e2e": {"value": B * a.steps / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * a.hidden, "d2h_bytes_per_step": 2 * a.hidden},
         }
         print(json.dumps(line), flush=True)
-    graph = None
-    run_step = None
     torch.cuda.synchronize()
     shutdown_process_group(dist if world > 1 else None)
+    if not ok:
+        sys.exit(3)
 
 
 def run_quantize(a):
@@ -615,6 +673,31 @@ def run_ours(a):
         per = sorted(s0.elapsed_time(s1) * 1e3 / rot for s0, s1 in evs)
         spread = {"median": per[len(per) // 2], "min": per[0], "max": per[-1], "steps_timed_singly": len(per)}
 
+    # the same ROT matvecs as ONE launch (lutgemm_sequence_run: a persistent kernel walks the list); m = 1 only
+    sequence = None
+    if rank == 0 and a.m == 1 and a.variant == 0 and not a.ordered:
+        try:
+            ops = [dict(w=w, in_kind=0, x_ext=x, out_kind=0, y_ext=torch.empty((1, a.n), dtype=torch.float16, device="cuda"))
+                   for w in weights]
+            seq = L.MatvecSequence(ops)
+            for _ in range(max(3, a.warmup)):
+                seq.run()
+            torch.cuda.synchronize()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(a.steps):
+                seq.run()
+            s1.record()
+            torch.cuda.synchronize()
+            us_seq = s0.elapsed_time(s1) * 1e3 / (a.steps * rot)
+            same = all(bool(torch.allclose(o["y_ext"].float(), y.float(), rtol=0, atol=2e-3 * float(y.float().abs().max())))
+                       for o, y in zip(ops, ys))
+            sequence = {"us_per_matvec": us_seq, "value": B / (us_seq * 1e-6) / 1e9, "unit": UNIT, "matvecs_per_launch": rot,
+                        "kernel": "gemv_seq_kernel", "device_status": seq.status(), "matches_per_call_results": same}
+            seq.close()
+        except Exception as e:
+            sequence = {"error": f"{type(e).__name__}: {e}"}
+
     # end to end through the host-buffer entry point
     e2e = None
     if not a.no_e2e:
@@ -672,6 +755,8 @@ def run_ours(a):
     }
     if e2e:
         line["e2e"] = e2e
+    if sequence:
+        line["sequence"] = sequence
     if a.m > 1:
         line["tensor_flops_per_matmul"] = 2.0 * a.m * a.n * a.k * (a.q + (1 if a.bias else 0))
         line["tensor_TFLOPs"] = line["tensor_flops_per_matmul"] / (us_per_gemv * 1e-6) / 1e12
@@ -696,6 +781,38 @@ def run_ours(a):
                                 "sample": "one full matvec, single thread as the reference is written "
                                           "(dequantize_cpu + serial-k fp32 matmul)", "seconds": dt,
                                 "max_abs_diff_vs_gpu_over_rms": float(np.abs(y_cpu - y_gpu).max() / rms)}
+    if world == 1 and a.m == 1 and not a.no_stack_tp1 and (a.n, a.k, a.q, a.g, a.bias) == (12288, 12288, 3, 128, False):
+        # the multi-GPU workload (the 96-layer decoder linear stack) on this one GPU: the anchor of the scaling curve
+        graph = None
+        run_step = None
+        for w in weights:
+            w.close()
+        weights = []
+        torch.cuda.synchronize()
+        try:
+            from lutgemm_b200 import tp_stack
+            st = make_stack(a, "seq", 0, 1, local)
+            xs_ = torch.from_numpy(synth.activations(1, a.hidden, seed=5).reshape(-1).view(np.int16).copy()).cuda().view(torch.float16)
+            st.x_in.copy_(xs_)
+            for _ in range(3):
+                st.step()
+            torch.cuda.synchronize()
+            n_st = max(5, min(a.steps, 30))
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(n_st):
+                st.step()
+            s1.record()
+            torch.cuda.synchronize()
+            ms_st = s0.elapsed_time(s1) / n_st
+            Bst = tp_stack.stack_algorithmic_bytes(a.hidden, a.ffn, a.q, a.g, a.layers)
+            line["stack_tp1"] = {"workload": f"decoder linear stack, {a.layers} layers, hidden {a.hidden}, ffn {a.ffn}, q={a.q} g={a.g} m=1, one GPU",
+                                 "ms_per_step": ms_st, "value": Bst / ms_st / 1e6, "unit": UNIT, "steps": n_st,
+                                 "algorithmic_bytes_per_step": Bst, "launches_per_step": 1, "device_status": st.device_status(),
+                                 "frac_of_peak": Bst / ms_st / 1e6 / peak}
+            st.close()
+        except Exception as e:
+            line["stack_tp1"] = {"error": f"{type(e).__name__}: {e}"}
     print(json.dumps(line), flush=True)
     graph = None
     run_step = None

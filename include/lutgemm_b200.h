@@ -82,23 +82,60 @@ int lutgemm_weight_destroy(lutgemm_weight_t w);
 int lutgemm_weight_describe(lutgemm_weight_t w, lutgemm_weight_desc* desc);
 
 /* out[m][N] (fp16, device) = in[m][K] (fp16, device) x W.
- * Replaces both lutGEMM::matmul overloads (lutGEMM/include/kernels.h:26-27,
- * lutGEMM/src/kernels.cu:56-71); q_bias is applied whenever the container has one, for every m.
- * Asynchronous on `stream` (a cudaStream_t, NULL = default stream); no host
- * synchronisation.  Calls that share one handle use the handle's split-k workspace and must
- * be ordered on one stream. */
+ * Replaces lutGEMM::matmul(output, input, nqW, m) (lutGEMM/include/kernels.h:27, lutGEMM/src/kernels.cu:64-71);
+ * q_bias is applied whenever the container has one, for every m.
+ * Asynchronous on `stream` (a cudaStream_t, NULL = default stream); no host synchronisation.
+ * The call uses the container's own split-k workspace, so calls that share a container must be ordered on one
+ * stream; to run one container from several streams at a time give every stream a workspace of its own
+ * (lutgemm_matmul_ws below).  A first batched call (m >= 4) on a container that was not told its batch size
+ * (lutgemm_weight_reserve_batch) allocates the batched path's fp32 rows, which synchronises the device; inside a
+ * stream capture that call fails with LUTGEMM_ERR_BATCH instead. */
 int lutgemm_matmul(void* out_fp16, const void* in_fp16, lutgemm_weight_t w, int m, void* stream);
 
 /* Same computation with the result left in fp32 (no final fp16 rounding). */
 int lutgemm_matmul_f32(float* out_f32, const void* in_fp16, lutgemm_weight_t w, int m, void* stream);
 
+/* The (output, nqW, input, n) overload of the reference (lutGEMM/include/kernels.h:26, lutGEMM/src/kernels.cu:56-63,
+ * 73-75; operand order of lutGEMM/src/cuda/kernels/cublas.h:47-55): W . X with the activations as COLUMNS,
+ * in[K][n] and out[N][n], both fp16 row-major.  For n == 1 these are the plain vectors of lutgemm_matmul.  For n > 1
+ * the library transposes in and out around the X . W kernels (two small extra launches) in scratch that belongs to
+ * the container (sized by lutgemm_weight_reserve_batch(w, n), else grown on first use as described above).
+ * The reference runs this overload on a dense weight laid out [N][K], i.e. on row-wise containers; here it is the same
+ * mathematical product for either container kind. */
+int lutgemm_matmul_wx(void* out_fp16, lutgemm_weight_t w, const void* in_fp16, int n, void* stream);
+
+/* Sizes everything lutgemm_matmul / lutgemm_matmul_wx / lutgemm_matmul_host may need for batches of up to m rows
+ * (fp32 split-k rows of the batched path, transposed copies of the W . X form), so that no later call allocates:
+ * call it once after creation, before capturing a CUDA graph that holds a batched call.  No reference counterpart
+ * (its scratch is a process-wide singleton grown inside the call, lutGEMM/src/cuda/tmpWeight.hpp:28-35). */
+int lutgemm_weight_reserve_batch(lutgemm_weight_t w, int m);
+
+/* An explicit split-k workspace: partial rows, arrival counters, a status word and the batched path's fp32 rows for
+ * containers up to max_n output features, max_k input features and batches up to max_m.  One workspace serves one
+ * stream at a time; two streams may run the SAME container concurrently when each passes its own workspace.
+ * lutgemm_matmul_ws / _f32_ws are lutgemm_matmul / _f32 on that workspace (NULL = the container's own) and never
+ * allocate: a container or batch beyond the workspace's sizes is refused with LUTGEMM_ERR_TOO_LARGE.
+ * lutgemm_workspace_status synchronises and reads the workspace's status word (see lutgemm_weight_device_status).
+ * No reference counterpart: the reference runs on the legacy default stream only. */
+typedef struct lutgemm_workspace* lutgemm_workspace_t;
+int lutgemm_workspace_create(lutgemm_workspace_t* out, int max_n, int max_k, int max_m);
+int lutgemm_workspace_destroy(lutgemm_workspace_t ws);
+int lutgemm_workspace_status(lutgemm_workspace_t ws, int* status);
+int lutgemm_matmul_ws(void* out_fp16, const void* in_fp16, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream);
+int lutgemm_matmul_f32_ws(float* out_f32, const void* in_fp16, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream);
+
 /* Same computation from and to HOST buffers: copies in (m*K fp16) to the device, runs,
  * copies out (m*N fp16) back and synchronises.  This is the call a host program holding
  * CPU activations makes (the reference test keeps them in managed memory,
- * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256).  (Letting the kernel read or write page-locked
+ * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256).  It runs on a non-blocking stream of the container's own;
+ * when a call passes the same two buffers and batch as the previous one (the usual pair of pinned staging buffers),
+ * copy-in, kernels and copy-out are replayed as one instantiated graph.  (Letting the kernel read or write page-locked
  * host buffers itself was measured: reading the activations across the bus costs 65 us per call against
- * 46-48 us with the two copies, and writing the results directly gains nothing.) */
+ * 46-48 us with the two copies, and writing the results directly gains nothing.)
+ * lutgemm_matmul_host_profile runs the same call once with events between its parts and returns, in microseconds,
+ * us4 = {copy in, kernels, copy out, all three on the device}. */
 int lutgemm_matmul_host(void* out_fp16_host, const void* in_fp16_host, lutgemm_weight_t w, int m);
+int lutgemm_matmul_host_profile(void* out_fp16_host, const void* in_fp16_host, lutgemm_weight_t w, int m, float* us4);
 
 /* Matvec (m = 1) that allocates nothing: out[N] (fp16) = in[K] (fp16) x W, with every array passed
  * by the caller as a device pointer in the container's layout (d_bW uint32 [K/32][q][N], d_alpha fp16
@@ -126,6 +163,11 @@ int lutgemm_matmul_host(void* out_fp16_host, const void* in_fp16_host, lutgemm_w
 int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uint32_t* d_bW,
                                   const void* d_alpha_fp16, const void* d_q_bias_fp16,
                                   int K, int N, int num_bits, int num_alpha_groups, void* stream);
+/* The status word of lutgemm_matvec_static_scratch lives in the same fixed array (that entry point has no
+ * container whose status could be asked): this call synchronises with the current device and reads it.
+ * 0 = the last call's bounded waits were all met; 1 / 2 = its weight stream stalled and the output is invalid.
+ * Each call of the entry point clears the word before its kernel.  No counterpart in the reference. */
+int lutgemm_static_scratch_status(int* status);
 
 /* ---- Tensor-parallel matvec: the exchange steps fused into the kernel (no counterpart in the reference,
  * which is single-GPU; lutGEMM/CMakeLists.txt:13 links no communication library). ----
@@ -227,6 +269,11 @@ int lutgemm_sequence_run(lutgemm_sequence_t s, void* stream);
 int lutgemm_sequence_status(lutgemm_sequence_t s, int* status);
 /* Time limit of one in-kernel wait for another matvec's or rank's data, in milliseconds (default 2000). */
 int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds);
+/* Tracing: with a device buffer of n_ops * ctas * 4 uint64 (ctas from lutgemm_sequence_describe) every later run
+ * records, per (matvec i, CTA c) at [(i * ctas + c) * 4 ..], the device clock in ns when (0) the CTA's activations had
+ * arrived, (1) its tables were built, (2) its last stage was consumed, (3) it left the matvec (bit 0 set if it was
+ * the one that published the column tile).  NULL switches tracing off.  Costs one predicated store per stamp. */
+int lutgemm_sequence_set_trace(lutgemm_sequence_t s, unsigned long long* d_stamps, size_t entries);
 /* Kernel launches one lutgemm_sequence_run makes (1) and the CTAs it uses; for reports. */
 int lutgemm_sequence_describe(lutgemm_sequence_t s, int* launches_per_run, int* ctas, size_t* exchange_bytes);
 int lutgemm_sequence_destroy(lutgemm_sequence_t s);
@@ -294,6 +341,18 @@ int lutgemm_bcq_quantize(const float* w, int N, int K, int q, int group_size, in
  * examples/utils.py:162-181): L values of +-1 <-> L/8 bytes, byte j = sum_i 2^i * [flat[i*L/8 + j] > 0]. */
 int lutgemm_packer_pack(const int8_t* flat_pm1, size_t L, uint8_t* packed);
 int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat_pm1);
+/* The same two mappings with both arrays on the current device (the reference's Packer runs its torch ops wherever
+ * the tensor lives, examples/utils.py:162-181). */
+int lutgemm_packer_pack_device(const int8_t* d_flat_pm1, size_t L, uint8_t* d_packed, void* stream);
+int lutgemm_packer_unpack_device(const uint8_t* d_packed, size_t L, int8_t* d_flat_pm1, void* stream);
+/* Device form of lutgemm_from_python_layout: the quantisers' tensors, already on the device, straight into the
+ * container layout in its final types (alpha and q_bias fp16), ready for lutgemm_weight_create_device.  The binary
+ * tensor [N][G][g][q] comes either as int8 +-1 (d_binary_py) or as the Packer's uint8 stream of the flattened tensor
+ * (d_binary_packed, N*K*q/8 bytes; examples/utils.py:162-172) - exactly one of the two - and in the packed case is
+ * read bit by bit without ever being expanded.  Group sizes are multiples of 32. */
+int lutgemm_from_python_layout_device(const float* d_alpha_py, const int8_t* d_binary_py, const uint8_t* d_binary_packed,
+                                      const float* d_offset_py, int N, int K, int g, int q, uint32_t* d_bW,
+                                      void* d_alpha_fp16, void* d_q_bias_fp16, void* stream);
 
 /* Text for a status code; never NULL. */
 const char* lutgemm_status_string(int status);
@@ -308,8 +367,9 @@ int lutgemm_set_gemv_ntile(int columns);
 int lutgemm_set_gemv_variant(int variant);
 /* 0 (default): the TMA-fed matvec adds its k-slabs with fp32 reductions in L2, whose order is not
  * fixed (results agree to fp32 rounding of a 24-term sum, then one fp16 rounding).  1: one partial
- * row per slab, added in slab order: bit-reproducible run to run, about 10 % slower.  Switch only
- * while no matvec is in flight.  (The reference's half2 atomicAdd accumulation,
+ * row per slab, added in slab order: bit-reproducible run to run, about 10 % slower; the batched
+ * (tensor-core) path then gives every column tile its whole k-range instead of reducing across k-ranges.
+ * Switch only while no matmul is in flight; a workspace may be used in either mode from call to call.  (The reference's half2 atomicAdd accumulation,
  * lutGEMM/src/cuda/kernels/mv_fp16.hpp:95, has no ordered mode.) */
 int lutgemm_set_ordered_reduction(int enabled);
 /* 1 (default): rows that go through the LUT matvec (m = 2, 3; any m with lutgemm_set_batched_path(0)) are taken

@@ -94,11 +94,12 @@ private:
     void* dense_ = nullptr;
 };
 
-// output[n? x mSize] = W-form call of the reference (output, nqW, input, n); same computation as below
-// for the layouts this library takes.  `algo` is accepted and ignored, as in the reference.
+// The W . X form (lutGEMM/include/kernels.h:26, lutGEMM/src/kernels.cu:56-63,73-75): input[kSize][n] and
+// output[mSize][n], fp16 row-major on the device, as the reference's cuBLAS call lays them out
+// (lutGEMM/src/cuda/kernels/cublas.h:47-55); for n == 1 plain vectors.  `algo` is accepted and ignored, as in the reference.
 inline void matmul(void* output, nQWeight_fp16& nqW, void* input, int n, int algo = 0) {
     (void)algo;
-    last_status_ref() = lutgemm_matmul(output, input, nqW.handle(), n, nullptr);
+    last_status_ref() = lutgemm_matmul_wx(output, nqW.handle(), input, n, nullptr);
 }
 // output[m][mSize] (fp16, device) = input[m][kSize] (fp16, device) x W.
 inline void matmul(void* output, void* input, nQWeight_fp16& nqW, int m, int algo = 0) {

@@ -94,6 +94,11 @@ class nQWeight_fp16:
             raise ValueError("empty nQWeight_fp16: call parsing() first")
         return self._h
 
+    def reserve_batch(self, m):
+        """Sizes the container's scratch for batches of up to m rows so that no later matmul allocates."""
+        capi.check(capi.lib().lutgemm_weight_reserve_batch(self.handle, int(m)), "reserve_batch")
+        return self
+
     def getDequantiedWeight(self, onGPU=True):
         """Dense fp16 weight as a torch CUDA tensor: [K, N] column-wise, [N, K] row-wise
         (lutGEMM/src/nQWeight_fp16.cu:93-99).  Only the GPU path exists here."""
@@ -118,21 +123,61 @@ class nQWeight_fp16:
             pass
 
 
-def matmul(output, input, nqW, m, algo=0, stream=None):
+class Workspace:
+    """Split-k scratch for one stream (lutgemm_workspace_*): pass one per stream to run a container from several
+    streams at once.  Serves containers up to max_n x max_k and batches up to max_m; never grows."""
+
+    def __init__(self, max_n, max_k, max_m=1):
+        self._h = C.c_void_p()
+        capi.check(capi.lib().lutgemm_workspace_create(C.byref(self._h), int(max_n), int(max_k), int(max_m)), "workspace_create")
+
+    @property
+    def handle(self):
+        return self._h
+
+    def status(self):
+        st = C.c_int(-1)
+        capi.check(capi.lib().lutgemm_workspace_status(self._h, C.byref(st)), "workspace_status")
+        return st.value
+
+    def close(self):
+        if self._h:
+            capi.lib().lutgemm_workspace_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def matmul(output, input, nqW, m, algo=0, stream=None, workspace=None):
     """output[m, N] (fp16 CUDA tensor) = input[m, K] (fp16 CUDA tensor) x W.  `algo` is accepted and
-    ignored, as in the reference (lutGEMM/src/cuda/kernels/mv_fp16.hpp:121-128)."""
-    capi.check(capi.lib().lutgemm_matmul(_ptr(output), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)), "matmul")
+    ignored, as in the reference (lutGEMM/src/cuda/kernels/mv_fp16.hpp:121-128).  workspace: a Workspace of the
+    calling stream's own (None = the container's)."""
+    if workspace is None:
+        capi.check(capi.lib().lutgemm_matmul(_ptr(output), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)), "matmul")
+    else:
+        capi.check(capi.lib().lutgemm_matmul_ws(_ptr(output), _ptr(input), nqW.handle, int(m), workspace.handle,
+                                                _stream_ptr(stream)), "matmul_ws")
     return output
 
 
 def matmul_wx(output, nqW, input, n, algo=0, stream=None):
-    """The (output, nqW, input, n) overload; the same computation for the layouts this library takes."""
-    return matmul(output, input, nqW, n, algo, stream)
+    """The (output, nqW, input, n) overload (lutGEMM/include/kernels.h:26): W . X with the activations as columns,
+    input [K, n] and output [N, n] fp16 CUDA tensors."""
+    capi.check(capi.lib().lutgemm_matmul_wx(_ptr(output), nqW.handle, _ptr(input), int(n), _stream_ptr(stream)), "matmul_wx")
+    return output
 
 
-def matmul_f32(output_f32, input, nqW, m, stream=None):
-    capi.check(capi.lib().lutgemm_matmul_f32(_ptr(output_f32), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)),
-               "matmul_f32")
+def matmul_f32(output_f32, input, nqW, m, stream=None, workspace=None):
+    if workspace is None:
+        capi.check(capi.lib().lutgemm_matmul_f32(_ptr(output_f32), _ptr(input), nqW.handle, int(m), _stream_ptr(stream)),
+                   "matmul_f32")
+    else:
+        capi.check(capi.lib().lutgemm_matmul_f32_ws(_ptr(output_f32), _ptr(input), nqW.handle, int(m), workspace.handle,
+                                                    _stream_ptr(stream)), "matmul_f32_ws")
     return output_f32
 
 
@@ -222,6 +267,37 @@ def packer_unpack(packed, L):
     return out
 
 
+def packer_pack_device(d_flat_pm1, stream=None):
+    """Packer.pack on the device: int8 +-1 CUDA tensor (any shape, flattened) -> uint8 CUDA tensor of size L / 8."""
+    import torch
+    flat = d_flat_pm1.contiguous().view(-1)
+    out = torch.empty(flat.numel() // 8, dtype=torch.uint8, device=flat.device)
+    capi.check(capi.lib().lutgemm_packer_pack_device(_ptr(flat), flat.numel(), _ptr(out), _stream_ptr(stream)), "packer_pack_device")
+    return out
+
+
+def packer_unpack_device(d_packed, L, stream=None):
+    import torch
+    out = torch.empty(L, dtype=torch.int8, device=d_packed.device)
+    capi.check(capi.lib().lutgemm_packer_unpack_device(_ptr(d_packed), L, _ptr(out), _stream_ptr(stream)), "packer_unpack_device")
+    return out
+
+
+def from_python_layout_device(d_alpha_py, d_binary, d_offset_py, N, K, g, q, packed=False, stream=None):
+    """The quantisers' tensors on the device (alpha float [N, G, q]; binary int8 [N, G, g, q], or with packed=True the
+    Packer's uint8 stream of it; offset float [N, G] or None) -> (bW int32 [K/32, q, N], alpha fp16 [G, q, N],
+    q_bias fp16 [G, N] or None) for nQWeight_fp16.from_device."""
+    import torch
+    dev = d_alpha_py.device
+    bW = torch.empty((K // 32, q, N), dtype=torch.int32, device=dev)
+    alpha = torch.empty((K // g, q, N), dtype=torch.float16, device=dev)
+    q_bias = None if d_offset_py is None else torch.empty((K // g, N), dtype=torch.float16, device=dev)
+    capi.check(capi.lib().lutgemm_from_python_layout_device(
+        _ptr(d_alpha_py), None if packed else _ptr(d_binary), _ptr(d_binary) if packed else None, _ptr(d_offset_py),
+        N, K, g, q, _ptr(bW), _ptr(alpha), _ptr(q_bias), _stream_ptr(stream)), "from_python_layout_device")
+    return bW, alpha, q_bias
+
+
 def bcq_quantize(w, qbits, rounds=15, group_size=-1):
     """The reference's quantize(w, qbits, rounds, group_size) (examples/bcq.py:23-98, unweighted defaults) on the GPU.
 
@@ -290,7 +366,7 @@ class MatvecSequence:
         for i, (kind, n) in enumerate(buffers):
             barr[i].kind, barr[i].n = int(kind), int(n)
         self._h = C.c_void_p()
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.n_ops = rank, world, len(ops)
         capi.check(lib.lutgemm_sequence_create(C.byref(self._h), arr, len(ops), barr, len(buffers), rank, world),
                    "sequence_create")
         if world > 1:
@@ -316,6 +392,19 @@ class MatvecSequence:
 
     def set_wait_limit(self, milliseconds):
         capi.check(capi.lib().lutgemm_sequence_set_wait_limit(self._h, int(milliseconds)), "sequence_set_wait_limit")
+
+    def trace(self, enable=True):
+        """Switches the per-(matvec, CTA) time stamps on (returns the int64 CUDA tensor [n_ops, ctas, 4] they land in,
+        device-clock ns; see lutgemm_sequence_set_trace) or off."""
+        if not enable:
+            capi.check(capi.lib().lutgemm_sequence_set_trace(self._h, None, 0), "sequence_set_trace")
+            self._trace = None
+            return None
+        import torch
+        ctas = self.describe()["ctas"]
+        self._trace = torch.zeros((self.n_ops, ctas, 4), dtype=torch.int64, device="cuda")
+        capi.check(capi.lib().lutgemm_sequence_set_trace(self._h, self._trace.data_ptr(), self._trace.numel()), "sequence_set_trace")
+        return self._trace
 
     def describe(self):
         a, b, c = C.c_int(), C.c_int(), C.c_size_t()

@@ -15,14 +15,18 @@ ERR_NULL, ERR_SHAPE, ERR_BITS, ERR_BATCH, ERR_CUDA, ERR_NO_DEVICE, ERR_TOO_LARGE
 # every symbol include/lutgemm_b200.h declares
 SYMBOLS = (
     "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
-    "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matvec_static_scratch", "lutgemm_dequantize",
+    "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matmul_host_profile", "lutgemm_matmul_wx",
+    "lutgemm_weight_reserve_batch", "lutgemm_workspace_create", "lutgemm_workspace_destroy", "lutgemm_workspace_status",
+    "lutgemm_matmul_ws", "lutgemm_matmul_f32_ws",
+    "lutgemm_matvec_static_scratch", "lutgemm_static_scratch_status", "lutgemm_dequantize",
     "lutgemm_matvec_tp", "lutgemm_matvec_tiles", "lutgemm_tp_finalize",
     "lutgemm_sequence_create", "lutgemm_sequence_export", "lutgemm_sequence_connect", "lutgemm_sequence_commit",
-    "lutgemm_sequence_run", "lutgemm_sequence_status", "lutgemm_sequence_set_wait_limit", "lutgemm_sequence_describe",
+    "lutgemm_sequence_run", "lutgemm_sequence_status", "lutgemm_sequence_set_wait_limit", "lutgemm_sequence_set_trace", "lutgemm_sequence_describe",
     "lutgemm_sequence_destroy",
     "lutgemm_ipc_alloc", "lutgemm_ipc_open", "lutgemm_ipc_close", "lutgemm_ipc_free",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
     "lutgemm_from_python_layout", "lutgemm_packer_pack", "lutgemm_packer_unpack",
+    "lutgemm_packer_pack_device", "lutgemm_packer_unpack_device", "lutgemm_from_python_layout_device",
     "lutgemm_bcq_quantize", "lutgemm_bcq_quantize_device", "lutgemm_matmul_gptq",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
     "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_ordered_reduction", "lutgemm_set_row_pairs", "lutgemm_weight_device_status",
@@ -84,6 +88,18 @@ def lib():
     L.lutgemm_matmul.argtypes = [vp, vp, vp, ip, vp]
     L.lutgemm_matmul_f32.argtypes = [vp, vp, vp, ip, vp]
     L.lutgemm_matmul_host.argtypes = [vp, vp, vp, ip]
+    L.lutgemm_matmul_host_profile.argtypes = [vp, vp, vp, ip, C.POINTER(C.c_float)]
+    L.lutgemm_matmul_wx.argtypes = [vp, vp, vp, ip, vp]
+    L.lutgemm_weight_reserve_batch.argtypes = [vp, ip]
+    L.lutgemm_workspace_create.argtypes = [C.POINTER(vp), ip, ip, ip]
+    L.lutgemm_workspace_destroy.argtypes = [vp]
+    L.lutgemm_workspace_status.argtypes = [vp, C.POINTER(ip)]
+    L.lutgemm_matmul_ws.argtypes = [vp, vp, vp, ip, vp, vp]
+    L.lutgemm_matmul_f32_ws.argtypes = [vp, vp, vp, ip, vp, vp]
+    L.lutgemm_static_scratch_status.argtypes = [C.POINTER(ip)]
+    L.lutgemm_packer_pack_device.argtypes = [vp, C.c_size_t, vp, vp]
+    L.lutgemm_packer_unpack_device.argtypes = [vp, C.c_size_t, vp, vp]
+    L.lutgemm_from_python_layout_device.argtypes = [vp, vp, vp, vp, ip, ip, ip, ip, vp, vp, vp, vp]
     L.lutgemm_matvec_static_scratch.argtypes = [vp, vp, vp, vp, vp, ip, ip, ip, ip, vp]
     L.lutgemm_dequantize.argtypes = [vp, vp, vp]
     L.lutgemm_matvec_tp.argtypes = [vp, vp, C.POINTER(TpLink), vp, vp, vp]
@@ -96,6 +112,7 @@ def lib():
     L.lutgemm_sequence_run.argtypes = [vp, vp]
     L.lutgemm_sequence_status.argtypes = [vp, C.POINTER(ip)]
     L.lutgemm_sequence_set_wait_limit.argtypes = [vp, ip]
+    L.lutgemm_sequence_set_trace.argtypes = [vp, vp, C.c_size_t]
     L.lutgemm_sequence_describe.argtypes = [vp, C.POINTER(ip), C.POINTER(ip), C.POINTER(C.c_size_t)]
     L.lutgemm_sequence_destroy.argtypes = [vp]
     L.lutgemm_ipc_alloc.argtypes = [C.c_size_t, C.POINTER(vp), vp]

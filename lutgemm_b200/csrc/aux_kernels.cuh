@@ -105,4 +105,66 @@ uniform_to_bcq_kernel(const float* __restrict__ scale, const float* __restrict__
     }
 }
 
+// The Python examples' uint8 interchange format (Packer.pack / Packer.unpack, examples/utils.py:162-181):
+// L values of +-1, byte j of the L/8 packed bytes = sum_i 2^i [flat[i L/8 + j] > 0].  One thread per byte:
+// eight strided reads (or writes), each coalesced across the warp.
+__global__ void __launch_bounds__(256)
+packer_pack_kernel(const int8_t* __restrict__ flat, size_t cols, uint8_t* __restrict__ packed) {
+    const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    unsigned v = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) v |= (flat[(size_t)i * cols + j] > 0 ? 1u : 0u) << i;
+    packed[j] = (uint8_t)v;
+}
+__global__ void __launch_bounds__(256)
+packer_unpack_kernel(const uint8_t* __restrict__ packed, size_t cols, int8_t* __restrict__ flat) {
+    const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    const unsigned v = packed[j];
+#pragma unroll
+    for (int i = 0; i < 8; i++) flat[(size_t)i * cols + j] = ((v >> i) & 1u) ? 1 : -1;
+}
+
+// The quantisers' tensors (alpha float [N][G][q], binary [N][G][g][q] of +-1, offset float [N][G] or null;
+// examples/bcq_parameter.py:41-48, examples/rtn_parameter.py:77-96) -> the container layout on the device:
+// bW [K/32][q][N], alpha fp16 [G][q][N], q_bias fp16 [G][N].  PACKED: the binary tensor arrives as Packer bytes
+// (element e of the flattened tensor is bit e / (L/8) of byte e % (L/8)) and is never expanded in memory.
+// One thread per (k-word, n): its 32 q signs are consecutive elements of the flattened tensor.
+template <bool PACKED>
+__global__ void __launch_bounds__(128)
+python_layout_kernel(const float* __restrict__ alpha_py, const void* __restrict__ binary, const float* __restrict__ offset_py,
+                     int N, int K, int g, int q, uint32_t* __restrict__ bW, __half* __restrict__ alpha,
+                     __half* __restrict__ q_bias) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    const int kw = blockIdx.y;
+    if (n >= N) return;
+    const int k = kw * 32, G = K / g, grp = k / g;
+    const size_t e0 = ((size_t)n * K + k) * q;                 // first element of this thread in the flattened tensor
+    const size_t cols = (size_t)N * K * q / 8;                 // PACKED: bytes in the stream
+    uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int t = 0; t < 32; t++) {
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            if (b < q) {
+                const size_t e = e0 + (size_t)t * q + b;
+                bool plus;
+                if (PACKED) {
+                    const size_t i = e / cols, j = e - i * cols;
+                    plus = (reinterpret_cast<const uint8_t*>(binary)[j] >> i) & 1u;
+                } else {
+                    plus = reinterpret_cast<const int8_t*>(binary)[e] > 0;
+                }
+                words[b] |= (plus ? 1u : 0u) << t;
+            }
+        }
+    }
+    for (int b = 0; b < q; b++) bW[((size_t)kw * q + b) * N + n] = words[b];
+    if (k == grp * g) {   // first word of the group moves the group's scales
+        const size_t ng = (size_t)n * G + grp;
+        for (int b = 0; b < q; b++) alpha[((size_t)grp * q + b) * N + n] = __float2half_rn(alpha_py[ng * q + b]);
+        if (offset_py) q_bias[(size_t)grp * N + n] = __float2half_rn(offset_py[ng]);
+    }
+}
+
 }  // namespace lg

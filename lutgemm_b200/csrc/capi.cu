@@ -22,6 +22,22 @@
 #include "bcq_quantize.cuh"
 #include "gptq3.cuh"
 
+// Split-k scratch of the matmul kernels: everything a call writes besides its output.  One per container by
+// default; lutgemm_workspace_create makes more, so that several streams can use one container at a time.
+struct lutgemm_workspace {
+    float* partial = nullptr;    // partial sums [slabs][n_cap] fp32 (ordered mode) / row 0 = zeroed L2 reduction row
+    float* partial2 = nullptr;   // second zeroed reduction row [n_cap] of the two-row matvec
+    unsigned* counters = nullptr;   // per-tile arrival counters, zero between launches
+    int* status = nullptr;       // device word set by a kernel whose bounded wait ran out
+    float* tc_partial = nullptr; // fp32 split-k rows of the batched (tensor-core) path, [tc_rows][n_cap], kept zeroed
+    int tc_rows = 0;
+    int n_cap = 0, slabs = 0;    // widest N and most 512-k slabs this workspace serves
+    // transposed copies for the (output, nqW, input, n) overload: input [n][K] and output [n][N] fp16
+    void* t_in = nullptr;
+    void* t_out = nullptr;
+    size_t t_in_bytes = 0, t_out_bytes = 0;
+};
+
 struct lutgemm_weight {
     uint32_t* bW = nullptr;
     __half* alpha = nullptr;
@@ -30,11 +46,8 @@ struct lutgemm_weight {
     bool row_wise = false;
     bool owns = true;
     int device = 0;
-    // split-k workspace: partial sums [ceil(K/512)][N] fp32 and per-tile arrival counters
-    float* partial = nullptr;
-    float* partial2 = nullptr;   // second zeroed reduction row [N] of the two-row matvec
-    unsigned* counters = nullptr;
-    int* status = nullptr;     // device word set by a kernel whose bounded wait ran out
+    // the container's own split-k workspace (calls that name no other workspace use it)
+    lutgemm_workspace own;
     // TMA descriptors of the packed planes and of alpha (valid when tma_ok)
     CUtensorMap tmW, tmA;
     bool tma_ok = false;
@@ -43,14 +56,19 @@ struct lutgemm_weight {
     // q_bias box {256, groups per 128 k} (valid when tc_ok)
     CUtensorMap tmWtc, tmAtc, tmQtc;
     bool tc_ok = false;
-    // fp32 split-k workspace of the batched (tensor-core) path, [tc_rows][N], grown on demand, kept zeroed
-    float* tc_partial = nullptr;
-    int tc_rows = 0;
     // staging for lutgemm_matmul_host
     void* h_stage_in = nullptr;
     void* d_stage_in = nullptr;
     void* d_stage_out = nullptr;
     size_t stage_rows = 0;
+    // lutgemm_matmul_host: its own non-blocking stream, and the last call's copy-run-copy sequence as an
+    // instantiated graph (relaunched while the caller keeps passing the same buffers and batch)
+    cudaStream_t host_stream = nullptr;
+    cudaGraphExec_t host_graph = nullptr;
+    const void* hg_in = nullptr;
+    void* hg_out = nullptr;
+    int hg_m = 0;
+    int hg_launches = 0;
 };
 
 struct lutgemm_sequence {
@@ -70,6 +88,7 @@ struct lutgemm_sequence {
     int a_rows = 1, wpg = 2, grid = 0;
     bool bias = false, committed = false;
     unsigned long long wait_ns = 2000000000ull;
+    unsigned long long* trace = nullptr;   // caller's device buffer, or null
 };
 
 namespace {
@@ -162,10 +181,11 @@ void make_tc_tensor_maps(lutgemm_weight* w, EncodeTiledFn enc) {
     w->tc_ok = true;
 }
 
-void make_tensor_maps(lutgemm_weight* w) {
+void make_tensor_maps(lutgemm_weight* w, bool with_batched = true) {
     w->tma_ok = false;
     w->tc_ok = false;
-    if (EncodeTiledFn e = encode_tiled_fn()) make_tc_tensor_maps(w, e);
+    if (with_batched)
+        if (EncodeTiledFn e = encode_tiled_fn()) make_tc_tensor_maps(w, e);
     const int g = w->g;
     if (w->N % 8 != 0 || !((lg::kSlab2 % g == 0) || (g % lg::kSlab2 == 0))) return;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -193,27 +213,56 @@ void make_tensor_maps(lutgemm_weight* w) {
     w->tma_ok = true;
 }
 
-int alloc_workspace(lutgemm_weight* w) {
-    make_tensor_maps(w);
-    const size_t nslabs = (size_t)(w->K + lg::kSlab2 - 1) / lg::kSlab2;
-    LG_CUDA(cudaMalloc(&w->partial, nslabs * (size_t)w->N * sizeof(float)));
-    LG_CUDA(cudaMemset(w->partial, 0, nslabs * (size_t)w->N * sizeof(float)));   // row 0 doubles as the reduction row
-    LG_CUDA(cudaMalloc(&w->partial2, (size_t)w->N * sizeof(float)));
-    LG_CUDA(cudaMemset(w->partial2, 0, (size_t)w->N * sizeof(float)));
-    LG_CUDA(cudaMalloc(&w->counters, kMaxCounters * sizeof(unsigned)));
-    LG_CUDA(cudaMemset(w->counters, 0, kMaxCounters * sizeof(unsigned)));
-    LG_CUDA(cudaMalloc(&w->status, sizeof(int)));
-    LG_CUDA(cudaMemset(w->status, 0, sizeof(int)));
+void free_workspace_buffers(lutgemm_workspace* ws) {
+    if (ws->partial) cudaFree(ws->partial);
+    if (ws->partial2) cudaFree(ws->partial2);
+    if (ws->counters) cudaFree(ws->counters);
+    if (ws->status) cudaFree(ws->status);
+    if (ws->tc_partial) cudaFree(ws->tc_partial);
+    if (ws->t_in) cudaFree(ws->t_in);
+    if (ws->t_out) cudaFree(ws->t_out);
+    *ws = lutgemm_workspace();
+}
+
+// Rows of the batched path's fp32 workspace for a batch of m (a multiple of 16, at most 128 per launch).
+int tc_rows_for(int m) {
+    const int rows = m > 128 ? 128 : m;
+    return (rows + 15) / 16 * 16;
+}
+
+int fill_workspace(lutgemm_workspace* ws, int N, int K, int batch_rows) {
+    const size_t nslabs = (size_t)(K + lg::kSlab2 - 1) / lg::kSlab2;
+    ws->n_cap = N; ws->slabs = (int)nslabs;
+    LG_CUDA(cudaMalloc(&ws->partial, nslabs * (size_t)N * sizeof(float)));
+    LG_CUDA(cudaMemset(ws->partial, 0, nslabs * (size_t)N * sizeof(float)));   // row 0 doubles as the reduction row
+    LG_CUDA(cudaMalloc(&ws->partial2, (size_t)N * sizeof(float)));
+    LG_CUDA(cudaMemset(ws->partial2, 0, (size_t)N * sizeof(float)));
+    LG_CUDA(cudaMalloc(&ws->counters, kMaxCounters * sizeof(unsigned)));
+    LG_CUDA(cudaMemset(ws->counters, 0, kMaxCounters * sizeof(unsigned)));
+    LG_CUDA(cudaMalloc(&ws->status, sizeof(int)));
+    LG_CUDA(cudaMemset(ws->status, 0, sizeof(int)));
+    if (batch_rows > 0) {
+        const int rows = tc_rows_for(batch_rows);
+        LG_CUDA(cudaMalloc(&ws->tc_partial, (size_t)rows * N * sizeof(float)));
+        LG_CUDA(cudaMemset(ws->tc_partial, 0, (size_t)rows * N * sizeof(float)));
+        ws->tc_rows = rows;
+    }
     return LUTGEMM_OK;
 }
 
+int alloc_workspace(lutgemm_weight* w) {
+    make_tensor_maps(w);
+    return fill_workspace(&w->own, w->N, w->K, 0);
+}
+
 int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
-    }
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev].load() > 0) return cached[dev].load();
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+    if (dev >= 0 && dev < 64) cached[dev].store(sms);
     return sms;
 }
 
@@ -311,11 +360,11 @@ void gemv_tma_geometry(const lutgemm_weight* w, int* nslabs, int* n_tile, int* t
     *tiles = (w->N + *n_tile - 1) / *n_tile;
 }
 
-int launch_gemv_tma_any(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, const lg::TpLink* link,
-                        cudaStream_t st) {
+int launch_gemv_tma_any(const lutgemm_weight* w, const lutgemm_workspace* ws, const __half* x, __half* y16, float* y32,
+                        const lg::TpLink* link, cudaStream_t st) {
     lg::Gemv2Params p2 = {};
     p2.bW = w->bW; p2.alpha = w->alpha; p2.q_bias = w->q_bias; p2.x = x;
-    p2.partial = w->partial; p2.counters = w->counters; p2.status = w->status; p2.y16 = y16; p2.y32 = y32;
+    p2.partial = ws->partial; p2.counters = ws->counters; p2.status = ws->status; p2.y16 = y16; p2.y32 = y32;
     p2.N = w->N; p2.K = w->K; p2.q = w->q; p2.g = w->g;
     int tiles = 0;
     gemv_tma_geometry(w, &p2.nslabs, &p2.n_tile, &tiles);
@@ -355,11 +404,11 @@ int launch_gemv_tma2(const lutgemm_weight* w, const lg::Gemv22Params& p, dim3 gr
 }
 
 // Two matvec rows in one pass over the weights (rows r and r + 1 of x / y); the caller has checked gemv_pair_ok().
-int gemv_pair(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
+int gemv_pair(const lutgemm_weight* w, const lutgemm_workspace* ws, const __half* x, __half* y16, float* y32, cudaStream_t st) {
     lg::Gemv22Params p = {};
     lg::Gemv2Params& b = p.b;
     b.bW = w->bW; b.alpha = w->alpha; b.q_bias = w->q_bias; b.x = x;
-    b.partial = w->partial; b.counters = w->counters; b.status = w->status; b.y16 = y16; b.y32 = y32;
+    b.partial = ws->partial; b.counters = ws->counters; b.status = ws->status; b.y16 = y16; b.y32 = y32;
     b.N = w->N; b.K = w->K; b.q = w->q; b.g = w->g;
     int tiles = 0;
     gemv_tma_geometry(w, &b.nslabs, &b.n_tile, &tiles);
@@ -367,26 +416,26 @@ int gemv_pair(const lutgemm_weight* w, const __half* x, __half* y16, float* y32,
     p.x1 = x + w->K;
     p.y16_1 = y16 ? y16 + w->N : nullptr;
     p.y32_1 = y32 ? y32 + w->N : nullptr;
-    p.partial1 = w->partial2;
+    p.partial1 = ws->partial2;
     dim3 grid(tiles, b.nslabs);
     const bool bias = w->q_bias != nullptr;
     if (w->g % 128 == 0) return launch_gemv_tma2<2>(w, p, grid, bias, st);
     return launch_gemv_tma2<1>(w, p, grid, bias, st);
 }
-bool gemv_pair_ok(const lutgemm_weight* w) {
-    return g_variant.load() == 0 && w->tma_ok && w->partial2 && !g_ordered.load() && g_pairs.load() &&
+bool gemv_pair_ok(const lutgemm_weight* w, const lutgemm_workspace* ws) {
+    return g_variant.load() == 0 && w->tma_ok && ws->partial2 && !g_ordered.load() && g_pairs.load() &&
            lg::gemv22_num_stages(w->a_rows) >= 2;
 }
 
 // One matvec row: y (fp16 and/or fp32) = x . W
-int gemv_row(const lutgemm_weight* w, const __half* x, __half* y16, float* y32, cudaStream_t st) {
+int gemv_row(const lutgemm_weight* w, const lutgemm_workspace* ws, const __half* x, __half* y16, float* y32, cudaStream_t st) {
     const bool use_tma = (g_variant.load() == 0) && w->tma_ok;
-    if (use_tma) return launch_gemv_tma_any(w, x, y16, y32, nullptr, st);
+    if (use_tma) return launch_gemv_tma_any(w, ws, x, y16, y32, nullptr, st);
     if (w->N % 4 == 0) {
         // register-fed kernel: any group size that is a multiple of 32
         lg::Gemv2Params p = {};
         p.bW = w->bW; p.alpha = w->alpha; p.q_bias = w->q_bias; p.x = x;
-        p.partial = w->partial; p.counters = w->counters; p.status = w->status; p.y16 = y16; p.y32 = y32;
+        p.partial = ws->partial; p.counters = ws->counters; p.status = ws->status; p.y16 = y16; p.y32 = y32;
         p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
         p.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
         p.n_tile = choose_ntile(w->N, p.nslabs, 1, lg::kStageCols);
@@ -431,7 +480,7 @@ int launch_gemm_tc_q(const lutgemm_weight* w, const CUtensorMap& tmX, const lg::
 }
 
 // Batched rows [0, m), m in 2..128, through the tensor-core kernel (container must have tc_ok).
-int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
+int gemm_tc_rows(lutgemm_weight* w, lutgemm_workspace* ws, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc || !w->tc_ok) return LUTGEMM_ERR_CUDA;
     lg::TcParams p = {};
@@ -460,20 +509,25 @@ int gemm_tc_rows(lutgemm_weight* w, const __half* x, __half* y16, float* y32, in
         const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
         if (eff > best + 0.02) { best = eff; splitk = c; }
     }
+    if (g_ordered.load()) splitk = 1;             // bit-reproducible mode: no unordered reductions across k-ranges
     p.steps_per_cta = (steps_total + splitk - 1) / splitk;
     splitk = (steps_total + p.steps_per_cta - 1) / p.steps_per_cta;
     if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
-    if (splitk > 1 && w->tc_rows < m) {
-        // grow the zeroed fp32 workspace (synchronises; happens once per container and batch size class)
-        if (w->tc_partial) LG_CUDA(cudaFree(w->tc_partial));
-        w->tc_partial = nullptr;
-        w->tc_rows = 0;
-        const int rows = (m + 15) / 16 * 16;
-        LG_CUDA(cudaMalloc(&w->tc_partial, (size_t)rows * w->N * sizeof(float)));
-        LG_CUDA(cudaMemset(w->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
-        w->tc_rows = rows;
+    if (splitk > 1 && ws->tc_rows < m) {
+        // Not reserved (lutgemm_weight_reserve_batch / lutgemm_workspace_create): only the container's own workspace
+        // grows by itself, which synchronises the device and cannot happen inside a stream capture.
+        if (ws != &w->own) return LUTGEMM_ERR_TOO_LARGE;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return LUTGEMM_ERR_BATCH;
+        if (ws->tc_partial) LG_CUDA(cudaFree(ws->tc_partial));
+        ws->tc_partial = nullptr;
+        ws->tc_rows = 0;
+        const int rows = tc_rows_for(m);
+        LG_CUDA(cudaMalloc(&ws->tc_partial, (size_t)rows * w->N * sizeof(float)));
+        LG_CUDA(cudaMemset(ws->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
+        ws->tc_rows = rows;
     }
-    p.partial = w->tc_partial; p.counters = w->counters; p.status = w->status;
+    p.partial = ws->tc_partial; p.counters = ws->counters; p.status = ws->status;
     p.y16 = y16; p.y32 = y32;
     p.N = w->N; p.K = w->K; p.g = w->g;
     dim3 grid(tiles, splitk);
@@ -516,10 +570,12 @@ int static_scratch_address(unsigned char** out) {
     return LUTGEMM_OK;
 }
 
-int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int m, void* stream) {
+int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int m, lutgemm_workspace* ws, void* stream) {
     if (!w || !in || (!y16 && !y32)) return LUTGEMM_ERR_NULL;
     if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
     if (((uintptr_t)in & 15) || ((uintptr_t)y16 & 15) || ((uintptr_t)y32 & 15)) return LUTGEMM_ERR_ALIGN;
+    if (!ws) ws = &w->own;
+    if (ws->n_cap < w->N || ws->slabs < (w->K + lg::kSlab2 - 1) / lg::kSlab2) return LUTGEMM_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
     const __half* x = (const __half*)in;
     // Up to three rows one LUT matvec per row is cheaper than the tensor-core kernel, whose cost is nearly
@@ -527,13 +583,13 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     // m x 17.6 us against 64 us).
     const int batched_mode = g_batched.load();
     if (m == 1 || batched_mode == 0 || (batched_mode == 1 && m < kBatchedFromRows) || !w->tc_ok) {
-        const bool pairs = gemv_pair_ok(w);
+        const bool pairs = gemv_pair_ok(w, ws);
         for (int r = 0; r < m;) {
             const int take = (pairs && r + 2 <= m) ? 2 : 1;
             const __half* xr = x + (size_t)r * w->K;
             __half* y16r = y16 ? y16 + (size_t)r * w->N : nullptr;
             float* y32r = y32 ? y32 + (size_t)r * w->N : nullptr;
-            int rc = take == 2 ? gemv_pair(w, xr, y16r, y32r, st) : gemv_row(w, xr, y16r, y32r, st);
+            int rc = take == 2 ? gemv_pair(w, ws, xr, y16r, y32r, st) : gemv_row(w, ws, xr, y16r, y32r, st);
             if (rc != LUTGEMM_OK) return rc;
             r += take;
         }
@@ -542,10 +598,37 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     // batched: 128 rows per tensor-core launch
     for (int r0 = 0; r0 < m; r0 += 128) {
         const int rows = (m - r0 < 128) ? (m - r0) : 128;
-        int rc = gemm_tc_rows(w, x + (size_t)r0 * w->K, y16 ? y16 + (size_t)r0 * w->N : nullptr,
+        int rc = gemm_tc_rows(w, ws, x + (size_t)r0 * w->K, y16 ? y16 + (size_t)r0 * w->N : nullptr,
                               y32 ? y32 + (size_t)r0 * w->N : nullptr, rows, st);
         if (rc != LUTGEMM_OK) return rc;
     }
+    return LUTGEMM_OK;
+}
+
+// fp16 [rows][cols] -> [cols][rows] through a 32 x 32 shared-memory tile (both sides coalesced)
+__global__ void __launch_bounds__(256)
+transpose_fp16_kernel(const __half* __restrict__ src, __half* __restrict__ dst, int rows, int cols) {
+    __shared__ __half tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[i][threadIdx.x] = src[(size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int c = c0 + i, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][i];
+    }
+}
+
+int grow(void** buf, size_t* have, size_t need, cudaStream_t st) {
+    if (*have >= need) return LUTGEMM_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return LUTGEMM_ERR_BATCH;
+    if (*buf) LG_CUDA(cudaFree(*buf));
+    *buf = nullptr; *have = 0;
+    LG_CUDA(cudaMalloc(buf, need));
+    *have = need;
     return LUTGEMM_OK;
 }
 
@@ -577,6 +660,7 @@ int launch_sequence(lutgemm_sequence* s, cudaStream_t st) {
     }
     lg::SeqParams& p = *s->params;
     p.wait_ns = s->wait_ns;
+    p.trace = s->trace;
     // cooperative launch: the runtime guarantees that all CTAs are resident together (they wait on one another),
     // or refuses the launch
     void* args[] = {&p};
@@ -667,11 +751,9 @@ int lutgemm_weight_destroy(lutgemm_weight_t w) {
         if (w->alpha) cudaFree(w->alpha);
         if (w->q_bias) cudaFree(w->q_bias);
     }
-    if (w->partial) cudaFree(w->partial);
-    if (w->partial2) cudaFree(w->partial2);
-    if (w->counters) cudaFree(w->counters);
-    if (w->status) cudaFree(w->status);
-    if (w->tc_partial) cudaFree(w->tc_partial);
+    free_workspace_buffers(&w->own);
+    if (w->host_graph) cudaGraphExecDestroy(w->host_graph);
+    if (w->host_stream) cudaStreamDestroy(w->host_stream);
     if (w->h_stage_in) cudaFreeHost(w->h_stage_in);
     if (w->d_stage_in) cudaFree(w->d_stage_in);
     if (w->d_stage_out) cudaFree(w->d_stage_out);
@@ -689,18 +771,105 @@ int lutgemm_weight_describe(lutgemm_weight_t w, lutgemm_weight_desc* d) {
 
 int lutgemm_matmul(void* out, const void* in, lutgemm_weight_t w, int m, void* stream) {
     if (!out) return LUTGEMM_ERR_NULL;
-    return matmul_impl((__half*)out, nullptr, in, w, m, stream);
+    return matmul_impl((__half*)out, nullptr, in, w, m, nullptr, stream);
 }
 
 int lutgemm_matmul_f32(float* out, const void* in, lutgemm_weight_t w, int m, void* stream) {
     if (!out) return LUTGEMM_ERR_NULL;
-    return matmul_impl(nullptr, out, in, w, m, stream);
+    return matmul_impl(nullptr, out, in, w, m, nullptr, stream);
 }
 
-int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w, int m) {
-    if (!w || !out_host || !in_host) return LUTGEMM_ERR_NULL;
+int lutgemm_matmul_ws(void* out, const void* in, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream) {
+    if (!out) return LUTGEMM_ERR_NULL;
+    return matmul_impl((__half*)out, nullptr, in, w, m, ws, stream);
+}
+
+int lutgemm_matmul_f32_ws(float* out, const void* in, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream) {
+    if (!out) return LUTGEMM_ERR_NULL;
+    return matmul_impl(nullptr, out, in, w, m, ws, stream);
+}
+
+int lutgemm_workspace_create(lutgemm_workspace_t* out, int max_n, int max_k, int max_m) {
+    if (!out) return LUTGEMM_ERR_NULL;
+    if (max_n < 1 || max_k < 32 || max_m < 1 || max_m > kMaxBatch) return LUTGEMM_ERR_SHAPE;
+    lutgemm_workspace* ws = new (std::nothrow) lutgemm_workspace();
+    if (!ws) return LUTGEMM_ERR_TOO_LARGE;
+    int rc = fill_workspace(ws, max_n, max_k, max_m >= 2 ? max_m : 0);
+    if (rc != LUTGEMM_OK) {
+        free_workspace_buffers(ws);
+        delete ws;
+        return rc;
+    }
+    *out = ws;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_workspace_destroy(lutgemm_workspace_t ws) {
+    if (!ws) return LUTGEMM_OK;
+    free_workspace_buffers(ws);
+    delete ws;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_workspace_status(lutgemm_workspace_t ws, int* status) {
+    if (!ws || !status) return LUTGEMM_ERR_NULL;
+    LG_CUDA(cudaMemcpy(status, ws->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return LUTGEMM_OK;
+}
+
+int lutgemm_weight_reserve_batch(lutgemm_weight_t w, int m) {
+    if (!w) return LUTGEMM_ERR_NULL;
     if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    lutgemm_workspace* ws = &w->own;
+    const int rows = tc_rows_for(m);
+    if (m >= 2 && ws->tc_rows < rows) {
+        if (ws->tc_partial) LG_CUDA(cudaFree(ws->tc_partial));
+        ws->tc_partial = nullptr; ws->tc_rows = 0;
+        LG_CUDA(cudaMalloc(&ws->tc_partial, (size_t)rows * w->N * sizeof(float)));
+        LG_CUDA(cudaMemset(ws->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
+        ws->tc_rows = rows;
+    }
+    // transposed copies of the (output, nqW, input, n) overload
+    int rc = grow(&ws->t_in, &ws->t_in_bytes, (size_t)m * w->K * sizeof(__half), nullptr);
+    if (rc == LUTGEMM_OK) rc = grow(&ws->t_out, &ws->t_out_bytes, (size_t)m * w->N * sizeof(__half), nullptr);
+    return rc;
+}
+
+int lutgemm_matmul_wx(void* out, lutgemm_weight_t w, const void* in, int n, void* stream) {
+    if (!out || !w || !in) return LUTGEMM_ERR_NULL;
+    if (n < 1 || n > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    if (n == 1) return matmul_impl((__half*)out, nullptr, in, w, 1, nullptr, stream);   // [K][1] and [N][1] are plain vectors
+    if (((uintptr_t)in & 15) || ((uintptr_t)out & 15)) return LUTGEMM_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    lutgemm_workspace* ws = &w->own;
+    int rc = grow(&ws->t_in, &ws->t_in_bytes, (size_t)n * w->K * sizeof(__half), st);
+    if (rc == LUTGEMM_OK) rc = grow(&ws->t_out, &ws->t_out_bytes, (size_t)n * w->N * sizeof(__half), st);
+    if (rc != LUTGEMM_OK) return rc;
+    // input [K][n] -> [n][K]; X.W; output [n][N] -> [N][n]
+    dim3 tb(32, 8);
+    transpose_fp16_kernel<<<dim3((n + 31) / 32, (w->K + 31) / 32), tb, 0, st>>>((const __half*)in, (__half*)ws->t_in, w->K, n);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    rc = matmul_impl((__half*)ws->t_out, nullptr, ws->t_in, w, n, ws, stream);
+    if (rc != LUTGEMM_OK) return rc;
+    transpose_fp16_kernel<<<dim3((w->N + 31) / 32, (n + 31) / 32), tb, 0, st>>>((const __half*)ws->t_out, (__half*)out, n, w->N);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+// The copy-in / run / copy-out sequence of lutgemm_matmul_host on `st`.
+static int host_sequence(lutgemm_weight_t w, void* out_host, const void* in_host, int m, cudaStream_t st) {
+    LG_CUDA(cudaMemcpyAsync(w->d_stage_in, in_host, (size_t)m * w->K * sizeof(__half), cudaMemcpyHostToDevice, st));
+    int rc = matmul_impl((__half*)w->d_stage_out, nullptr, w->d_stage_in, w, m, nullptr, st);
+    if (rc != LUTGEMM_OK) return rc;
+    LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+    return LUTGEMM_OK;
+}
+
+static int host_prepare(lutgemm_weight_t w, int m) {
+    if (!w->host_stream) LG_CUDA(cudaStreamCreateWithFlags(&w->host_stream, cudaStreamNonBlocking));
     if (w->stage_rows < (size_t)m) {
+        if (w->host_graph) { cudaGraphExecDestroy(w->host_graph); w->host_graph = nullptr; }
         if (w->d_stage_in) cudaFree(w->d_stage_in);
         if (w->d_stage_out) cudaFree(w->d_stage_out);
         w->d_stage_in = w->d_stage_out = nullptr;
@@ -708,13 +877,75 @@ int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w,
         LG_CUDA(cudaMalloc(&w->d_stage_in, (size_t)m * w->K * sizeof(__half)));
         LG_CUDA(cudaMalloc(&w->d_stage_out, (size_t)m * w->N * sizeof(__half)));
         w->stage_rows = (size_t)m;
+        int rc = lutgemm_weight_reserve_batch(w, m);
+        if (rc != LUTGEMM_OK) return rc;
     }
-    LG_CUDA(cudaMemcpyAsync(w->d_stage_in, in_host, (size_t)m * w->K * sizeof(__half), cudaMemcpyHostToDevice, 0));
-    int rc = matmul_impl((__half*)w->d_stage_out, nullptr, w->d_stage_in, w, m, nullptr);
-    if (rc != LUTGEMM_OK) return rc;
-    LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, 0));
-    LG_CUDA(cudaStreamSynchronize(0));
     return LUTGEMM_OK;
+}
+
+int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w, int m) {
+    if (!w || !out_host || !in_host) return LUTGEMM_ERR_NULL;
+    if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    int rc = host_prepare(w, m);
+    if (rc != LUTGEMM_OK) return rc;
+    cudaStream_t st = w->host_stream;
+    if (w->host_graph && w->hg_in == in_host && w->hg_out == out_host && w->hg_m == m) {
+        // the same buffers and batch as last time: one graph launch replays copy-in, kernels and copy-out
+        LG_CUDA(cudaGraphLaunch(w->host_graph, st));
+        g_launches.fetch_add((unsigned long long)w->hg_launches, std::memory_order_relaxed);
+        LG_CUDA(cudaStreamSynchronize(st));
+        return LUTGEMM_OK;
+    }
+    rc = host_sequence(w, out_host, in_host, m, st);
+    if (rc != LUTGEMM_OK) return rc;
+    LG_CUDA(cudaStreamSynchronize(st));
+    // record the sequence for the next call with these buffers (capture runs nothing)
+    if (w->host_graph) { cudaGraphExecDestroy(w->host_graph); w->host_graph = nullptr; }
+    const unsigned long long before = g_launches.load();
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int rc2 = host_sequence(w, out_host, in_host, m, st);
+        const cudaError_t e = cudaStreamEndCapture(st, &graph);
+        if (rc2 == LUTGEMM_OK && e == cudaSuccess && graph &&
+            cudaGraphInstantiate(&w->host_graph, graph, 0) == cudaSuccess) {
+            w->hg_in = in_host; w->hg_out = out_host; w->hg_m = m;
+            w->hg_launches = (int)(g_launches.load() - before);
+        } else {
+            w->host_graph = nullptr;
+            (void)cudaGetLastError();
+        }
+        if (graph) cudaGraphDestroy(graph);
+        g_launches.store(before);                 // captured launches did not run
+    } else {
+        (void)cudaGetLastError();
+    }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_matmul_host_profile(void* out_host, const void* in_host, lutgemm_weight_t w, int m, float* us4) {
+    if (!w || !out_host || !in_host || !us4) return LUTGEMM_ERR_NULL;
+    if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
+    int rc = host_prepare(w, m);
+    if (rc != LUTGEMM_OK) return rc;
+    cudaStream_t st = w->host_stream;
+    cudaEvent_t ev[4];
+    for (int i = 0; i < 4; i++) LG_CUDA(cudaEventCreate(&ev[i]));
+    LG_CUDA(cudaEventRecord(ev[0], st));
+    LG_CUDA(cudaMemcpyAsync(w->d_stage_in, in_host, (size_t)m * w->K * sizeof(__half), cudaMemcpyHostToDevice, st));
+    LG_CUDA(cudaEventRecord(ev[1], st));
+    rc = matmul_impl((__half*)w->d_stage_out, nullptr, w->d_stage_in, w, m, nullptr, st);
+    if (rc == LUTGEMM_OK) {
+        LG_CUDA(cudaEventRecord(ev[2], st));
+        LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+        LG_CUDA(cudaEventRecord(ev[3], st));
+        LG_CUDA(cudaStreamSynchronize(st));
+        float ms = 0.f;
+        for (int i = 0; i < 3; i++) { LG_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1])); us4[i] = ms * 1e3f; }
+        LG_CUDA(cudaEventElapsedTime(&ms, ev[0], ev[3]));
+        us4[3] = ms * 1e3f;
+    }
+    for (int i = 0; i < 4; i++) cudaEventDestroy(ev[i]);
+    return rc;
 }
 
 int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uint32_t* d_bW, const void* d_alpha_fp16,
@@ -735,7 +966,7 @@ int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uin
     w.q_bias = (__half*)const_cast<void*>(d_q_bias_fp16);
     w.N = N; w.K = K; w.q = num_bits; w.G = num_alpha_groups; w.g = K / num_alpha_groups;
     w.owns = false;
-    make_tensor_maps(&w);
+    make_tensor_maps(&w, false);                                // the two matvec descriptors only
     if (!w.tma_ok) return LUTGEMM_ERR_SHAPE;                    // needs N % 8 == 0 and a group size the TMA kernel takes
     unsigned char* scratch = nullptr;
     rc = static_scratch_address(&scratch);
@@ -761,6 +992,15 @@ int lutgemm_matvec_static_scratch(void* out_fp16, const void* in_fp16, const uin
     const bool bias = d_q_bias_fp16 != nullptr;
     if (w.g % 128 == 0) return launch_gemv_tma<2>(&w, p, grid, bias, st);
     return launch_gemv_tma<1>(&w, p, grid, bias, st);
+}
+
+int lutgemm_static_scratch_status(int* status) {
+    if (!status) return LUTGEMM_ERR_NULL;
+    unsigned char* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != LUTGEMM_OK) return rc;
+    LG_CUDA(cudaMemcpy(status, scratch + kStaticRowBytes + kStaticCounterBytes, sizeof(int), cudaMemcpyDeviceToHost));
+    return LUTGEMM_OK;
 }
 
 int lutgemm_matvec_tiles(lutgemm_weight_t w, int* tiles) {
@@ -792,7 +1032,7 @@ int lutgemm_matvec_tp(const void* in_fp16, lutgemm_weight_t w, const lutgemm_tp_
         if (link->out_mode != 0 && !link->flag_out[r]) return LUTGEMM_ERR_NULL;
         t.out16[r] = (__half*)link->out16[r]; t.out32[r] = link->out32[r]; t.flag_out[r] = link->flag_out[r];
     }
-    return launch_gemv_tma_any(w, (const __half*)in_fp16, (__half*)out_fp16, out_f32, &t, (cudaStream_t)stream);
+    return launch_gemv_tma_any(w, &w->own, (const __half*)in_fp16, (__half*)out_fp16, out_f32, &t, (cudaStream_t)stream);
 }
 
 int lutgemm_tp_finalize(void* out_fp16, float* out_f32, const float* slots, int slot_stride, int world, int n,
@@ -800,7 +1040,7 @@ int lutgemm_tp_finalize(void* out_fp16, float* out_f32, const float* slots, int 
     if ((!out_fp16 && !out_f32) || !slots || !flag_in || !status_owner) return LUTGEMM_ERR_NULL;
     if (world < 1 || world > 8 || n < 1) return LUTGEMM_ERR_SHAPE;
     lg::tp_finalize_kernel<<<1, 256, 0, (cudaStream_t)stream>>>((__half*)out_fp16, out_f32, slots, slot_stride, world, n,
-                                                                 flag_in, flag_target, status_owner->status);
+                                                                 flag_in, flag_target, status_owner->own.status);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     LG_CUDA(cudaGetLastError());
     return LUTGEMM_OK;
@@ -1012,6 +1252,13 @@ int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds) {
     return LUTGEMM_OK;
 }
 
+int lutgemm_sequence_set_trace(lutgemm_sequence_t s, unsigned long long* d_stamps, size_t entries) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    if (d_stamps && entries < s->h_ops.size() * (size_t)s->grid * 4) return LUTGEMM_ERR_SHAPE;
+    s->trace = d_stamps;
+    return LUTGEMM_OK;
+}
+
 int lutgemm_sequence_describe(lutgemm_sequence_t s, int* launches_per_run, int* ctas, size_t* exchange_bytes) {
     if (!s) return LUTGEMM_ERR_NULL;
     if (launches_per_run) *launches_per_run = 1;
@@ -1171,6 +1418,51 @@ int lutgemm_packer_unpack(const uint8_t* packed, size_t L, int8_t* flat) {
     return LUTGEMM_OK;
 }
 
+int lutgemm_packer_pack_device(const int8_t* d_flat, size_t L, uint8_t* d_packed, void* stream) {
+    if (!d_flat || !d_packed) return LUTGEMM_ERR_NULL;
+    if (L == 0 || L % 8 != 0) return LUTGEMM_ERR_SHAPE;
+    const size_t cols = L / 8;
+    if ((cols + 255) / 256 > 0x7fffffffull) return LUTGEMM_ERR_TOO_LARGE;
+    lg::packer_pack_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_flat, cols, d_packed);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_packer_unpack_device(const uint8_t* d_packed, size_t L, int8_t* d_flat, void* stream) {
+    if (!d_flat || !d_packed) return LUTGEMM_ERR_NULL;
+    if (L == 0 || L % 8 != 0) return LUTGEMM_ERR_SHAPE;
+    const size_t cols = L / 8;
+    if ((cols + 255) / 256 > 0x7fffffffull) return LUTGEMM_ERR_TOO_LARGE;
+    lg::packer_unpack_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_packed, cols, d_flat);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+int lutgemm_from_python_layout_device(const float* d_alpha_py, const int8_t* d_binary_py, const uint8_t* d_binary_packed,
+                                      const float* d_offset_py, int N, int K, int g, int q, uint32_t* d_bW,
+                                      void* d_alpha_fp16, void* d_q_bias_fp16, void* stream) {
+    if (!d_alpha_py || (!d_binary_py && !d_binary_packed) || (d_binary_py && d_binary_packed) || !d_bW || !d_alpha_fp16)
+        return LUTGEMM_ERR_NULL;
+    if (d_offset_py && !d_q_bias_fp16) return LUTGEMM_ERR_NULL;
+    if (N < 1 || K < 32 || K % 32 != 0 || g < 32 || g % 32 != 0 || K % g != 0) return LUTGEMM_ERR_SHAPE;
+    if (q < 1 || q > 8) return LUTGEMM_ERR_BITS;
+    if (d_binary_packed && ((size_t)N * K * q) % 8 != 0) return LUTGEMM_ERR_SHAPE;
+    dim3 grid((N + 127) / 128, K / 32);
+    if (grid.y > 65535) return LUTGEMM_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d_binary_packed)
+        lg::python_layout_kernel<true><<<grid, 128, 0, st>>>(d_alpha_py, d_binary_packed, d_offset_py, N, K, g, q, d_bW,
+                                                              (__half*)d_alpha_fp16, (__half*)d_q_bias_fp16);
+    else
+        lg::python_layout_kernel<false><<<grid, 128, 0, st>>>(d_alpha_py, d_binary_py, d_offset_py, N, K, g, q, d_bW,
+                                                               (__half*)d_alpha_fp16, (__half*)d_q_bias_fp16);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
 int lutgemm_matmul_gptq(int m, int n, int k_packed, const void* scale_fp16, const void* zero_fp16,
                         const void* in_fp16, const uint32_t* mat, void* out_fp16, void* stream) {
     if (!scale_fp16 || !zero_fp16 || !in_fp16 || !mat || !out_fp16) return LUTGEMM_ERR_NULL;
@@ -1273,7 +1565,7 @@ const char* lutgemm_status_string(int s) {
 
 int lutgemm_weight_device_status(lutgemm_weight_t w, int* status) {
     if (!w || !status) return LUTGEMM_ERR_NULL;
-    LG_CUDA(cudaMemcpy(status, w->status, sizeof(int), cudaMemcpyDeviceToHost));
+    LG_CUDA(cudaMemcpy(status, w->own.status, sizeof(int), cudaMemcpyDeviceToHost));
     return LUTGEMM_OK;
 }
 

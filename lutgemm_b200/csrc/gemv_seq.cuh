@@ -26,6 +26,10 @@
 
 namespace lg {
 
+#ifndef LG_TRACE_FINISH
+#define LG_TRACE_FINISH 0
+#endif
+constexpr bool getenv_dbg = LG_TRACE_FINISH;
 constexpr int kSeqThreads = kGemv2Threads;                   // 16 consumer warps + 1 producer warp
 constexpr int kSeqMaxOps = 896;                              // matvecs per sequence (their geometry travels as kernel parameters)
 constexpr int kSeqXsOff = kXchgOff + 1024;                   // 512 fp16 activations of the current slab
@@ -73,6 +77,7 @@ struct SeqParams {
     unsigned* done;          // CTAs that have finished this step
     int* status;
     unsigned long long wait_ns;   // time limit of a poll loop
+    unsigned long long* trace;    // optional: 4 time stamps (ns) per (matvec, CTA), see lutgemm_sequence_set_trace
     SeqGeo geo[kSeqMaxOps];
 };
 
@@ -433,25 +438,32 @@ gemv_seq_kernel(const __grid_constant__ SeqParams p) {
             const int n_begin = tile * n_tile;
             const int n_end = min(N, n_begin + n_tile);
             // the slab's activations (waits for whoever produces them), then the tables
+            unsigned long long* tr = (p.trace && tid == 0 && it == cta) ? p.trace + ((size_t)j * ncta + cta) * 4 : nullptr;
             seq_fetch_input(op, k0, seq, xs, tid, p);
+            if (tr) tr[0] = global_ns();
             build_lut_from_raw(lut, *reinterpret_cast<const uint4*>(xs + 16 * lut_chunk_of(tid)), tid);
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+            if (tr) tr[1] = global_ns();
 
             seq_consume_item<WPG, BIAS>(slot, round, aborted, n_begin, n_end, k0, G.q, G.g, G.K, N, op.partial, op.q_bias, p.a_rows, p.status);
 
             // split-k finish: the last CTA of the column tile publishes it
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+            if (tr) tr[2] = global_ns();
             if (tid == 0) {
                 __threadfence();
                 const unsigned prev = atomicAdd(op.counters + tile, 1u);
                 *s_flag = (prev == (unsigned)nslabs - 1u);
                 if (prev == (unsigned)nslabs - 1u) op.counters[tile] = 0u;
+                if (tr && getenv_dbg) tr[0] = global_ns();
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
+            if (tr && getenv_dbg) tr[1] = global_ns();
             if (*s_flag) {
                 __threadfence();
                 seq_publish(op, n_begin, n_end, seq, tid);
             }
+            if (tr) tr[3] = global_ns() | (*s_flag ? 1ull : 0ull);      // bit 0: this CTA published the tile
             // (the barrier of the next seq_fetch_input keeps s_flag and the tables apart from the next item)
         }
     }

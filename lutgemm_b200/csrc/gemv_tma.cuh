@@ -275,6 +275,9 @@ __device__ __forceinline__ void splitk_finish(const Gemv2Params& p, int tid, int
             const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sl * rowN));
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
+        // Row 0 is also the L2 reduction row of the default mode, which expects to find it zero: leave it so, so
+        // that the mode may be switched between calls on one workspace.
+        if (p.ordered) __stcg(reinterpret_cast<float4*>(p.partial + c), make_float4(0.f, 0.f, 0.f, 0.f));
         __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
         uint2 o;
         o.x = *reinterpret_cast<uint32_t*>(&lo);

@@ -33,7 +33,9 @@ int main() {
     cudaDeviceSynchronize();
     if (lutGEMM::last_status() != 0) { printf("matmul failed: %s\n", lutgemm_status_string(lutGEMM::last_status())); return 1; }
 
-    double max_diff = 0;
+    // the X.W call against a host fp32 evaluation: max relative error (floor 1e-2 rms) <= 1e-2, mean absolute error <= 1e-3
+    std::vector<float> ref(N);
+    double rms = 0;
     for (int n = 0; n < N; n++) {
         float acc = 0;
         for (int k = 0; k < K; k++) {
@@ -44,11 +46,36 @@ int main() {
             }
             acc += x[k] * w;
         }
-        max_diff = std::fmax(max_diff, std::fabs(acc - __half2float(d_out[n])));
+        ref[n] = acc;
+        rms += (double)acc * acc;
     }
+    rms = std::sqrt(rms / N);
+    double max_rel = 0, mae = 0;
+    for (int n = 0; n < N; n++) {
+        const double d = std::fabs(ref[n] - __half2float(d_out[n]));
+        max_rel = std::fmax(max_rel, d / std::fmax(std::fabs((double)ref[n]), 1e-2 * rms));
+        mae += d / N;
+    }
+    // the W.X overload with n = 4 columns: input [K][4], output [N][4]; column c carries 2^(c-2) * x (exact in fp16)
+    const int NC = 4;
+    __half *d_in2, *d_out2;
+    cudaMallocManaged(&d_in2, sizeof(__half) * K * NC);
+    cudaMallocManaged(&d_out2, sizeof(__half) * N * NC);
+    for (int k = 0; k < K; k++)
+        for (int c = 0; c < NC; c++) d_in2[k * NC + c] = __float2half(x[k] * 0.25f * (float)(1 << c));
+    lutGEMM::matmul((void*)d_out2, nqW, (void*)d_in2, NC);
+    cudaDeviceSynchronize();
+    double max_rel2 = 0;
+    for (int n = 0; n < N; n++)
+        for (int c = 0; c < NC; c++) {
+            const double want = ref[n] * 0.25 * (double)(1 << c);
+            const double d = std::fabs(want - __half2float(d_out2[n * NC + c]));
+            max_rel2 = std::fmax(max_rel2, d / std::fmax(std::fabs(want), 1e-2 * rms));
+        }
     std::vector<__half> dense((size_t)K * N);
     lutGEMM::dequantize_cpu(nqW, dense.data());
-    printf("shim ok %.3e fields %d %d %d %d %d\n", max_diff, nqW.mSize, nqW.kSize, nqW.nb, nqW.num_groups, nqW.group_size);
-    cudaFree(d_in); cudaFree(d_out);
-    return (max_diff < 5e-3 && lutGEMM::last_status() == 0) ? 0 : 1;
+    printf("shim ok %.3e %.3e wx %.3e fields %d %d %d %d %d\n", max_rel, mae, max_rel2, nqW.mSize, nqW.kSize, nqW.nb, nqW.num_groups,
+           nqW.group_size);
+    cudaFree(d_in); cudaFree(d_out); cudaFree(d_in2); cudaFree(d_out2);
+    return (max_rel <= 1e-2 && mae <= 1e-3 && max_rel2 <= 1e-2 && lutGEMM::last_status() == 0) ? 0 : 1;
 }

@@ -4,7 +4,8 @@ Some hosts cannot call cudaMalloc once they are up (all device memory already be
 pool, or their rules forbid it); for them the library keeps the split-k workspace in a fixed array of
 its own image.  This test calls that entry point through the C ABI, twice in a row on the same
 arrays, and checks both results against the ordinary entry point (lutgemm_matmul) on the same
-container data, within the tolerance the other parity tests use.  It sits last in collection order so
+container data and against the CPU oracle, within the tolerance the other parity tests use, and reads the
+entry point's status word (it lives in the same fixed array).  It sits last in collection order so
 that a run which stops at the first failure has already run every other test; it passes alone in a
 fresh process as well.
 """
@@ -15,6 +16,7 @@ import pytest
 
 import lutgemm_b200 as L
 from lutgemm_b200 import capi, synth
+from oracle import oracle
 from parity_utils import MAE, MAX_REL, error_metrics
 
 pytestmark = pytest.mark.gpu
@@ -38,6 +40,7 @@ def test_static_scratch_matches_ordinary_entry_point_twice(N, K, q, g, bias):
     L.matmul(want, xd, w, 1)
     torch.cuda.synchronize()
     want = want.float().cpu().numpy()
+    ref = oracle.bcq_matmul_fp32(x, bW, alpha.astype(np.float16), None if qb is None else qb.astype(np.float16), g)
     # the same data as plain device arrays for the non-allocating entry point
     d_bW = _dev(bW.view(np.int32), torch.int32)
     d_alpha = _dev(alpha.astype(np.float16).view(np.int16), torch.float16)
@@ -53,6 +56,10 @@ def test_static_scratch_matches_ordinary_entry_point_twice(N, K, q, g, bias):
         assert np.isfinite(got).all(), f"call {call}"
         rel, mae = error_metrics(got, want)
         assert rel <= MAX_REL and mae <= MAE, (call, rel, mae)
+        rel_o, mae_o = error_metrics(got, ref)                 # and directly against the reference's host evaluation
+        assert rel_o <= MAX_REL and mae_o <= MAE, (call, rel_o, mae_o)
+        st = C.c_int(-1)
+        assert lib.lutgemm_static_scratch_status(C.byref(st)) == capi.OK and st.value == 0, (call, st.value)
         # both paths round the same fp32 sums once; only the unordered slab additions may differ
         step = np.spacing(np.abs(want).astype(np.float16)).astype(np.float32)
         assert np.all(np.abs(got - want) <= step + 4e-6 * float(np.sqrt((want ** 2).mean()))), f"call {call}"
