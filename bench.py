@@ -38,9 +38,9 @@ from lutgemm_b200 import synth  # noqa: E402
 METRIC = "bcq_gemv_effective_bandwidth"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tma_kernel launch at the default bench shape
-# (N = K = 12288, q = 3, g = 128, m = 1), from the ncu capture summarised in
-# profiles/gemv_tma_kernel_12288x12288_q3_g128.md: 63 803 392 + 163 584 bytes.
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv_tma_kernel launch at the default bench shape
+# (N = K = 12288, q = 3, g = 128, m = 1), from an ncu capture of this very command; to be captured again
+# whenever that kernel changes (a run under ncu is never a bench value, so the figure is carried here).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 63966976
 
 
@@ -198,6 +198,7 @@ def run_reference(a):
             "warmup": warm, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(a), "matvecs_per_step": 1},
+            "steps_requested": a.steps, "warmup_requested": a.warmup, "steps_capped_at": 5, "warmup_capped_at": 1,
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind,
                              "sample": "one full matvec per step: dequantize_cpu on k-slabs + serial-k fp32 matmul"},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -577,6 +578,69 @@ def run_gptq(a):
     print(json.dumps(line))
 
 
+def batched_numbers(local):
+    """Config 4's batched corner on this GPU: n = k = 8192, q = 2, g = 64 at m = 16 and m = 128 through lutgemm_matmul (the
+    tcgen05 kernel), CUDA-graph replay over 8 weight sets, with the reference's own batched path (dequantise + cuBLAS,
+    child process) beside it.  Returns the dict for the bench line's "batched" key."""
+    import torch
+    import lutgemm_b200 as L
+    n = k = 8192
+    q, g, rot = 2, 64, 8
+    out = {"workload": f"bcq_gemm n={n} k={k} q={q} g={g}", "kernel": "gemm_tc_kernel"}
+    ws = []
+    for i in range(rot):
+        bW, alpha, _ = synth.bcq_layer(n, k, q, g, seed=synth.seed_for("bench", n, k, q, i))
+        ws.append(L.nQWeight_fp16(bW, alpha, k, n, q, False, k // g).reserve_batch(128))
+    for m in (16, 128):
+        xh = synth.activations(m, k, seed=77)
+        x = torch.from_numpy(xh.view(np.int16)).cuda().view(torch.float16)
+        y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        def step():
+            for w in ws:
+                L.matmul(y, x, w, m)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 50
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * rot)
+        flops = 2.0 * m * n * k * q
+        row = {"us": us, "plane_wise_TFLOPs": flops / (us * 1e-6) / 1e12,
+               "hbm_GBps": synth.algorithmic_bytes(n, k, q, g, m, False) / (us * 1e-6) / 1e9}
+        try:
+            child = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--n", str(n), "--k", str(k),
+                                    "--q", str(q), "--g", str(g), "--m", str(m), "--rot", "4", "--steps", "5"],
+                                   capture_output=True, text=True, timeout=180)
+            rows = [l for l in child.stdout.splitlines() if l.startswith("{")]
+            ref = json.loads(rows[-1])["reference_gpu"] if rows else None
+            if ref:
+                row["reference_gpu_us"] = ref["us_per_matvec"]
+                row["reference_gpu_mae"] = ref["mae_vs_fp32_host"]
+        except Exception:
+            pass
+        del graph
+        out[f"m{m}"] = row
+    for w in ws:
+        w.close()
+    return out
+
+
 def run_ours(a):
     import torch
     import lutgemm_b200 as L
@@ -720,6 +784,23 @@ def run_ours(a):
             dt = float(t.item())
         e2e = {"value": world * a.steps * rot * B / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": rot * 2 * a.k * a.m,
                "d2h_bytes_per_step": rot * 2 * a.n * a.m, "us_per_matvec": dt / (a.steps * rot) * 1e6}
+        # where a call's time goes: events between copy-in, kernels and copy-out on the call's own stream (one call,
+        # run without the replayed graph), and the host wall clock of the ordinary call around them
+        try:
+            import ctypes as C
+            us4 = (C.c_float * 4)()
+            prof = []
+            for _ in range(20):
+                capi.check(lib.lutgemm_matmul_host_profile(yout.data_ptr(), xin.data_ptr(), weights[0].handle, a.m, us4), "matmul_host_profile")
+                prof.append(list(us4))
+            med = [sorted(p[i] for p in prof)[len(prof) // 2] for i in range(4)]
+            e2e["breakdown_us"] = {"h2d": med[0], "kernels": med[1], "d2h": med[2], "device_total": med[3],
+                                   "host_wall_per_call": e2e["us_per_matvec"],
+                                   "launch_and_sync": e2e["us_per_matvec"] - med[3],
+                                   "note": "host_wall is the replayed-graph call (copy-in, kernels, copy-out as one graph launch + one stream "
+                                           "synchronise on a non-blocking stream); the parts are from one unreplayed call with events"}
+        except Exception as e:
+            e2e["breakdown_us"] = {"error": f"{type(e).__name__}: {e}"}
         # the result that came back is the device result (up to one fp16 step: the split-k reductions are unordered)
         got = yout.numpy().view(np.float16).astype(np.float32)
         want = ys[-1].float().cpu().numpy()
@@ -782,6 +863,10 @@ def run_ours(a):
                                           "(dequantize_cpu + serial-k fp32 matmul)", "seconds": dt,
                                 "max_abs_diff_vs_gpu_over_rms": float(np.abs(y_cpu - y_gpu).max() / rms)}
     if world == 1 and a.m == 1 and not a.no_stack_tp1 and (a.n, a.k, a.q, a.g, a.bias) == (12288, 12288, 3, 128, False):
+        try:
+            line["batched"] = batched_numbers(local)
+        except Exception as e:
+            line["batched"] = {"error": f"{type(e).__name__}: {e}"}
         # the multi-GPU workload (the 96-layer decoder linear stack) on this one GPU: the anchor of the scaling curve
         graph = None
         run_step = None

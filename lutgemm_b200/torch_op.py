@@ -20,10 +20,12 @@ import torch
 
 from . import api
 
+import weakref
+
 _containers = {}      # (device index, data pointers, shapes) -> nQWeight_fp16 wrapping the tensors without a copy
 
 
-def _container(bW, alpha, q_bias):
+def _container(bW, alpha, q_bias, reserve_rows=0):
     key = (bW.device.index, bW.data_ptr(), alpha.data_ptr(), 0 if q_bias is None else q_bias.data_ptr(),
            tuple(bW.shape), tuple(alpha.shape))
     w = _containers.get(key)
@@ -33,14 +35,29 @@ def _container(bW, alpha, q_bias):
         with torch.cuda.device(bW.device):
             w = api.nQWeight_fp16.from_device(bW, alpha, q_bias, kw * 32, N, q, False, G, copy=False)
         _containers[key] = w
+        # the container (and the workspace it allocated) goes when the weight tensor it wraps goes: after module.to(),
+        # a reload of the weights or deletion of the module nothing stays behind
+        weakref.finalize(bW, _drop, key)
+    if reserve_rows > 1:
+        with torch.cuda.device(bW.device):
+            w.reserve_batch(reserve_rows)
     return w
 
 
+def _drop(key):
+    w = _containers.pop(key, None)
+    if w is not None:
+        try:
+            w._keep = None
+            w.close()
+        except Exception:
+            pass
+
+
 def release_containers():
-    """Drops every cached container (call after freeing the weight tensors they wrap)."""
-    for w in _containers.values():
-        w.close()
-    _containers.clear()
+    """Drops every cached container now (they are otherwise dropped when their weight tensor is collected)."""
+    for key in list(_containers):
+        _drop(key)
 
 
 def _check(x, bW, alpha, q_bias):
@@ -75,13 +92,22 @@ def _(x, bW, alpha, q_bias):
 class BCQLinear(torch.nn.Module):
     """y = x W^T with W [N, K] held as q bit planes and per-group scales (plus an optional per-group offset)."""
 
-    def __init__(self, bW, alpha, q_bias=None):
+    def __init__(self, bW, alpha, q_bias=None, max_batch=0):
         super().__init__()
         self.register_buffer("bW", bW)
         self.register_buffer("alpha", alpha)
         self.register_buffer("q_bias", q_bias)
         self.in_features, self.out_features = bW.shape[0] * 32, bW.shape[2]
         self.num_bits, self.num_groups = bW.shape[1], alpha.shape[0]
+        self.max_batch = max_batch
+
+    def reserve(self, rows=None):
+        """Sizes the container's scratch for batches of up to `rows` activation rows now, so that no forward call
+        allocates (needed before a forward with more than 3 rows is captured into a CUDA graph)."""
+        rows = self.max_batch if rows is None else rows
+        if self.bW.is_cuda and rows > 1:
+            _container(self.bW, self.alpha, self.q_bias, reserve_rows=rows)
+        return self
 
     @classmethod
     def from_kernel_layout(cls, bW_u32, alpha_f32, q_bias_f32=None, device="cuda"):

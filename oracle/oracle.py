@@ -29,15 +29,25 @@ _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
+def _makefile_default_ref():
+    """The default of the Makefile's REF variable (one place holds the path)."""
+    for line in open(os.path.join(_HERE, "Makefile")):
+        if line.startswith("REF") and "?=" in line:
+            return line.split("?=", 1)[1].strip()
+    return ""
+
+
 def build(force=False):
     """Compile the C restatement (and oracle/_ref when the reference tree exists)."""
     so = os.path.join(_HERE, "liblutgemm_oracle.so")
     src = os.path.join(_HERE, "lutgemm_oracle.c")
     stale = (not os.path.exists(so)) or os.path.getmtime(so) < os.path.getmtime(src)
-    ref_missing = os.path.isdir("/root/reference/lutGEMM/src") and not os.path.exists(
+    ref = os.environ.get("REF", "")                   # the Makefile's variable: where the reference tree lies (its default otherwise)
+    ref_dir = ref or _makefile_default_ref()
+    ref_missing = os.path.isdir(os.path.join(ref_dir, "lutGEMM", "src")) and not os.path.exists(
         os.path.join(_HERE, "_ref", "libref_cpu.so"))
     if force or stale or ref_missing:
-        subprocess.check_call(["make", "-s", "-C", _HERE] + (["-B"] if force else []))
+        subprocess.check_call(["make", "-s", "-C", _HERE] + (["-B"] if force else []) + (["REF=" + ref] if ref else []))
     return so
 
 

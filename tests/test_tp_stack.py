@@ -87,6 +87,88 @@ def test_two_rank_stack_over_gloo_matches_single_rank(tmp_path):
         assert float(f["err"]) <= 2e-3 * float(f["scale"]) + 1e-3   # fp16 roundings of the intermediate vectors only
 
 
+SEQ_WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["LG_ROOT"])
+from lutgemm_b200 import synth, tp_stack, tp_seq
+from oracle import oracle
+
+# A host model of what lutgemm_sequence_run does with the list tp_seq.stack_program builds: exchange buffers that every
+# rank fills on every rank (fp16 vectors, one fp32 row per rank), consumers that add the rows in rank order and round
+# once.  The "stores into every rank's copy" are an all_gather of what each rank produced, placed by the PRODUCER's
+# out_off (taken from that rank's own program).
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+H, F, Q, G, LAYERS = 256, 512, 2, 64, 2
+def host_container(bW, alpha, n_loc, k_loc):
+    return {"bW": bW, "alpha": alpha.astype(np.float16)}
+def mv(out, x, w):
+    y = oracle.bcq_matmul_fp32(x.numpy().reshape(1, -1), w["bW"], w["alpha"], None, G)
+    out.copy_(torch.from_numpy(y.reshape(-1)).to(out.dtype))
+st = tp_stack.TPLinearStack(H, F, Q, G, LAYERS, rank=rank, world=world, device="cpu", seed=3,
+                            matvec=mv, matvec_f32=mv, make_container=host_container, generate="host")
+programs = [tp_seq.stack_program(H, F, LAYERS, r, world) for r in range(world)]
+buffers, ops = programs[rank]
+vec = {b: np.zeros(n, np.float16) for b, (kind, n) in enumerate(buffers) if kind == 1}
+rows = {b: np.zeros((world, n), np.float32) for b, (kind, n) in enumerate(buffers) if kind == 2}
+x = synth.activations(1, H, seed=9).reshape(-1).copy()
+result = None
+for i, o in enumerate(ops):
+    w = None if o["idx"] is None else st.weights[o["layer"]][o["idx"]]
+    K = o["n"] if w is None else w["bW"].shape[0] * 32
+    off = o.get("in_off", 0)
+    if o["in_kind"] == 0:
+        xin = x
+    elif o["in_kind"] == 1:
+        xin = vec[o["in_buf"]][off:off + K]
+    else:
+        acc = np.zeros(K, np.float32)
+        for r in range(world):                       # rank order, one rounding
+            acc += rows[o["in_buf"]][r, off:off + K]
+        xin = acc.astype(np.float16)
+    if w is None:
+        result = xin.copy()
+        continue
+    y = oracle.bcq_matmul_fp32(xin.reshape(1, -1), w["bW"], w["alpha"], None, G).reshape(-1)
+    N = y.size
+    if o["out_kind"] == 1:
+        mine = torch.from_numpy(y.astype(np.float16).astype(np.float32))     # fp16 values, carried exactly in fp32
+        got = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(got, mine)
+        for r in range(world):
+            ro = programs[r][1][i]["out_off"]
+            vec[o["out_buf"]][ro:ro + N] = got[r].numpy().astype(np.float16)
+    else:
+        mine = torch.from_numpy(y.astype(np.float32).copy())
+        got = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(got, mine)
+        for r in range(world):
+            rows[o["out_buf"]][r, o.get("out_off", 0):o.get("out_off", 0) + N] = got[r].numpy()
+want = st.step(torch.from_numpy(x)).numpy()          # the same shards through gloo collectives
+err = float(np.abs(result.astype(np.float32) - want.astype(np.float32)).max()); scale = float(np.abs(want.astype(np.float32)).max())
+print(f"RESULT rank={rank} err={err:.3e} scale={scale:.3e} ops={len(ops)} buffers={len(buffers)}", flush=True)
+dist.destroy_process_group()
+'''
+
+
+def test_sequence_program_of_the_stack_over_gloo_matches_collectives(tmp_path):
+    """The list of matvecs and exchange buffers that the one-launch stack hands to lutgemm_sequence_create, executed by a
+    host model of the exchange on two CPU ranks, against the same shards run through gloo all-gather / all-reduce."""
+    script = tmp_path / "seq_worker.py"
+    script.write_text(SEQ_WORKER)
+    env = dict(os.environ, LG_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29617", WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
+        line = [l for l in o.splitlines() if l.startswith("RESULT")][0]
+        f = dict(kv.split("=") for kv in line.split()[1:])
+        assert f["ops"] == "9" and f["buffers"] == "8"
+        assert float(f["err"]) <= 1e-3 * float(f["scale"]) + 1e-4   # same roundings in both; only summation order differs
+
+
 @pytest.mark.gpu
 def test_single_gpu_stack_matches_host_chain():
     torch = pytest.importorskip("torch")
