@@ -127,11 +127,11 @@ int lutgemm_matmul_f32_ws(float* out_f32, const void* in_fp16, lutgemm_weight_t 
 /* Same computation from and to HOST buffers: copies in (m*K fp16) to the device, runs,
  * copies out (m*N fp16) back and synchronises.  This is the call a host program holding
  * CPU activations makes (the reference test keeps them in managed memory,
- * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256).  It runs on a non-blocking stream of the container's own;
- * when a call passes the same two buffers and batch as the previous one (the usual pair of pinned staging buffers),
- * copy-in, kernels and copy-out are replayed as one instantiated graph.  (Letting the kernel read or write page-locked
- * host buffers itself was measured: reading the activations across the bus costs 65 us per call against
- * 46-48 us with the two copies, and writing the results directly gains nothing.)
+ * tests/opt/fp16/int3_col_wise_matmul_fp16.cu:246-256).  It runs on a non-blocking stream of the container's own.
+ * m = 1 with both buffers page-locked (cudaHostAlloc / cudaHostRegister, 16-byte aligned): no copy engine is involved;
+ * one kernel reads the activations from the host buffer (each CTA the 1 KB its k-slab needs, while its weight stream
+ * starts) and stores the result into the host buffer.  Otherwise: copy-in, kernels, copy-out, replayed as one
+ * instantiated graph while the caller keeps passing the same two buffers and batch.
  * lutgemm_matmul_host_profile runs the same call once with events between its parts and returns, in microseconds,
  * us4 = {copy in, kernels, copy out, all three on the device}. */
 int lutgemm_matmul_host(void* out_fp16_host, const void* in_fp16_host, lutgemm_weight_t w, int m);

@@ -69,6 +69,11 @@ struct lutgemm_weight {
     void* hg_out = nullptr;
     int hg_m = 0;
     int hg_launches = 0;
+    // page-locked buffers: the copy engine and the stream synchronisation are replaced by a fetch kernel, result
+    // stores straight into the host buffer and a completion word in page-locked memory that the host polls
+    bool hg_pinned = false;
+    volatile unsigned* h_done = nullptr;   // page-locked, 64 B
+    unsigned* d_done = nullptr;            // its device alias
 };
 
 struct lutgemm_sequence {
@@ -621,6 +626,21 @@ transpose_fp16_kernel(const __half* __restrict__ src, __half* __restrict__ dst, 
     }
 }
 
+// Host-buffer call, page-locked buffers: the activations come over the bus through this kernel instead of the copy
+// engine (whose 24 KB copy costs ~8 us of fixed latency), ...
+__global__ void __launch_bounds__(1024)
+host_fetch_kernel(const uint4* __restrict__ src_host, uint4* __restrict__ dst, int n16) {
+    lg::pdl_launch_dependents();                       // the matvec behind it may start streaming its weights
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) dst[i] = src_host[i];
+}
+// ... and completion is a word in page-locked memory written behind the last kernel, which the host polls: that
+// takes a bus write instead of the driver's synchronisation path (~15 us).
+__global__ void host_done_kernel(unsigned* done_host, unsigned value) {
+    lg::pdl_wait_prior_grids();                        // every kernel before it has finished and flushed
+    __threadfence_system();
+    *reinterpret_cast<volatile unsigned*>(done_host) = value;
+}
+
 int grow(void** buf, size_t* have, size_t need, cudaStream_t st) {
     if (*have >= need) return LUTGEMM_OK;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -752,6 +772,7 @@ int lutgemm_weight_destroy(lutgemm_weight_t w) {
         if (w->q_bias) cudaFree(w->q_bias);
     }
     free_workspace_buffers(&w->own);
+    if (w->h_done) cudaFreeHost((void*)w->h_done);
     if (w->host_graph) cudaGraphExecDestroy(w->host_graph);
     if (w->host_stream) cudaStreamDestroy(w->host_stream);
     if (w->h_stage_in) cudaFreeHost(w->h_stage_in);
@@ -857,12 +878,45 @@ int lutgemm_matmul_wx(void* out, lutgemm_weight_t w, const void* in, int n, void
     return LUTGEMM_OK;
 }
 
-// The copy-in / run / copy-out sequence of lutgemm_matmul_host on `st`.
-static int host_sequence(lutgemm_weight_t w, void* out_host, const void* in_host, int m, cudaStream_t st) {
+// The copy-in / run / copy-out sequence of lutgemm_matmul_host on `st`.  d_in / d_out: device aliases of the buffers
+// when both are page-locked (then no copy engine: a fetch kernel, the result stored straight to the host buffer by the
+// kernels' last CTAs, and the completion word), else null.
+static int host_sequence(lutgemm_weight_t w, void* out_host, const void* in_host, int m, cudaStream_t st, void* d_in, void* d_out) {
+    if (d_in && d_out) {
+        const int n16 = (int)((size_t)m * w->K * sizeof(__half) / 16);
+        host_fetch_kernel<<<(n16 + 1023) / 1024 > 8 ? 8 : (n16 + 1023) / 1024, 1024, 0, st>>>((const uint4*)d_in, (uint4*)w->d_stage_in, n16);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        int rc = matmul_impl((__half*)d_out, nullptr, w->d_stage_in, w, m, nullptr, st);
+        if (rc != LUTGEMM_OK) return rc;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1); cfg.blockDim = dim3(1); cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        LG_CUDA(cudaLaunchKernelEx(&cfg, host_done_kernel, w->d_done, 1u));
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return LUTGEMM_OK;
+    }
     LG_CUDA(cudaMemcpyAsync(w->d_stage_in, in_host, (size_t)m * w->K * sizeof(__half), cudaMemcpyHostToDevice, st));
     int rc = matmul_impl((__half*)w->d_stage_out, nullptr, w->d_stage_in, w, m, nullptr, st);
     if (rc != LUTGEMM_OK) return rc;
     LG_CUDA(cudaMemcpyAsync(out_host, w->d_stage_out, (size_t)m * w->N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+    return LUTGEMM_OK;
+}
+
+// Waits for the completion word (bounded: a few seconds of polling, then the ordinary synchronisation, which also
+// reports a failed kernel).
+static int host_wait(lutgemm_weight_t w, cudaStream_t st, bool pinned) {
+    if (pinned) {
+        for (long it = 0; it < 400000000L; it++) {
+            if (*w->h_done == 1u) return LUTGEMM_OK;
+#if defined(__x86_64__)
+            __builtin_ia32_pause();
+#endif
+        }
+    }
+    LG_CUDA(cudaStreamSynchronize(st));
     return LUTGEMM_OK;
 }
 
@@ -883,6 +937,14 @@ static int host_prepare(lutgemm_weight_t w, int m) {
     return LUTGEMM_OK;
 }
 
+// Device alias of a page-locked host pointer, or null when the memory is pageable / not 16-byte aligned.
+static void* pinned_alias(const void* p) {
+    if ((uintptr_t)p & 15) return nullptr;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w, int m) {
     if (!w || !out_host || !in_host) return LUTGEMM_ERR_NULL;
     if (m < 1 || m > kMaxBatch) return LUTGEMM_ERR_BATCH;
@@ -890,25 +952,41 @@ int lutgemm_matmul_host(void* out_host, const void* in_host, lutgemm_weight_t w,
     if (rc != LUTGEMM_OK) return rc;
     cudaStream_t st = w->host_stream;
     if (w->host_graph && w->hg_in == in_host && w->hg_out == out_host && w->hg_m == m) {
-        // the same buffers and batch as last time: one graph launch replays copy-in, kernels and copy-out
+        // the same buffers and batch as last time: one graph launch replays the whole call
+        if (w->hg_pinned) *w->h_done = 0u;
         LG_CUDA(cudaGraphLaunch(w->host_graph, st));
         g_launches.fetch_add((unsigned long long)w->hg_launches, std::memory_order_relaxed);
-        LG_CUDA(cudaStreamSynchronize(st));
-        return LUTGEMM_OK;
+        return host_wait(w, st, w->hg_pinned);
     }
-    rc = host_sequence(w, out_host, in_host, m, st);
+    void* d_in = pinned_alias(in_host);
+    void* d_out = pinned_alias(out_host);
+    if (!w->h_done) {
+        void* hp = nullptr;
+        if (cudaHostAlloc(&hp, 64, cudaHostAllocMapped) == cudaSuccess) {
+            w->h_done = (volatile unsigned*)hp;
+            void* dp = nullptr;
+            if (cudaHostGetDevicePointer(&dp, hp, 0) == cudaSuccess) w->d_done = (unsigned*)dp;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
+    const bool pinned = d_in && d_out && w->h_done && w->d_done && ((size_t)m * w->K * sizeof(__half)) % 16 == 0;
+    if (!pinned) d_in = d_out = nullptr;
+    if (pinned) *w->h_done = 0u;
+    rc = host_sequence(w, out_host, in_host, m, st, d_in, d_out);
     if (rc != LUTGEMM_OK) return rc;
-    LG_CUDA(cudaStreamSynchronize(st));
+    rc = host_wait(w, st, pinned);
+    if (rc != LUTGEMM_OK) return rc;
     // record the sequence for the next call with these buffers (capture runs nothing)
     if (w->host_graph) { cudaGraphExecDestroy(w->host_graph); w->host_graph = nullptr; }
     const unsigned long long before = g_launches.load();
     cudaGraph_t graph = nullptr;
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-        const int rc2 = host_sequence(w, out_host, in_host, m, st);
+        const int rc2 = host_sequence(w, out_host, in_host, m, st, d_in, d_out);
         const cudaError_t e = cudaStreamEndCapture(st, &graph);
         if (rc2 == LUTGEMM_OK && e == cudaSuccess && graph &&
             cudaGraphInstantiate(&w->host_graph, graph, 0) == cudaSuccess) {
-            w->hg_in = in_host; w->hg_out = out_host; w->hg_m = m;
+            w->hg_in = in_host; w->hg_out = out_host; w->hg_m = m; w->hg_pinned = pinned;
             w->hg_launches = (int)(g_launches.load() - before);
         } else {
             w->host_graph = nullptr;

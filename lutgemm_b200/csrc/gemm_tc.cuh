@@ -96,6 +96,11 @@ inline TcLayout tc_layout(int q, bool bias, int g, int m) {
     if (L.w_slots > kTcMaxSlots) L.w_slots = kTcMaxSlots;
     L.bar_off = kTcSmemTotal - kTcBarBytes;
     L.smem_bytes = kTcSmemTotal;
+    // The epilogue turns accumulator blocks through a per-warp scratch of 16 x 33 floats that starts at x_off and, for
+    // m_pad == 16 (activation ring 32 KB), reaches 1 KB into the first weight slot.  That is safe only because both rings
+    // are idle by then (the accumulators are complete when every load has been consumed) and the kernel walks one
+    // output tile per launch; the plan is refused if the scratch would ever leave the two rings.
+    if (kTcExpWarps * 16 * 33 * 4 > L.x_slots * L.x_slot_bytes + L.w_slots * L.w_slot_bytes) L.w_slots = 0;
     L.d_stride = L.m_pad <= 64 ? 64 : 128;
     L.a_stages = L.m_pad <= 64 ? 3 : 2;                    // 2 * d_stride + 128 * a_stages = 512 columns
     L.permute_x = L.m_pad <= 64 ? 1 : 0;
@@ -444,7 +449,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int lq = warp & 3, gi = (warp - kTcFirstExpWarp) >> 2, hN = gi & 1, hK = gi >> 1;
         const uint32_t t_src = tmem_base + ((uint32_t)(lq * 32) << 16) + kTcDCol + (uint32_t)(hN * L.d_stride);
         // A tcgen05.ld leaves lane = output column, register = activation row.  Each 16 x 32 block is turned through a
-        // per-warp scratch in shared memory (the activation ring, idle once the accumulators are complete; rows padded to
+        // per-warp scratch in shared memory (the activation ring and, for 16 rows, the first KB of the weight ring: both
+        // idle once the accumulators are complete, see tc_layout; rows padded to
         // 33 floats: no bank conflicts either way) so that a lane holds 4 consecutive columns of one row: vector
         // reductions / 128-bit stores, a quarter of the L2 transactions of scalar ones.
         float* scratch = reinterpret_cast<float*>(smem + L.x_off) + (warp - kTcFirstExpWarp) * (16 * 33);

@@ -26,10 +26,6 @@
 
 namespace lg {
 
-#ifndef LG_TRACE_FINISH
-#define LG_TRACE_FINISH 0
-#endif
-constexpr bool getenv_dbg = LG_TRACE_FINISH;
 constexpr int kSeqThreads = kGemv2Threads;                   // 16 consumer warps + 1 producer warp
 constexpr int kSeqMaxOps = 896;                              // matvecs per sequence (their geometry travels as kernel parameters)
 constexpr int kSeqXsOff = kXchgOff + 1024;                   // 512 fp16 activations of the current slab
@@ -411,8 +407,10 @@ gemv_seq_kernel(const __grid_constant__ SeqParams p) {
         }
     } else {
     // ---------------- consumers ----------------
-    int slot = 0, round = 0;
-    bool aborted = false;
+    // The ring position is re-derived per item from the count of stages consumed so far, which depends on the
+    // kernel's parameters only: the compiler can then see that it is the same in every lane (carried through the item
+    // loops it would inherit the divergence of the barrier polls inside them).
+    unsigned stages_done = 0;
     for (int j = 0; j < p.n_ops; j++) {
         const SeqGeo& G = p.geo[j];
         const int items = G.reduce_only ? (G.K + kSlab2 - 1) / kSlab2 : G.tiles * G.nslabs;
@@ -445,7 +443,10 @@ gemv_seq_kernel(const __grid_constant__ SeqParams p) {
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
             if (tr) tr[1] = global_ns();
 
+            int slot = (int)(stages_done % (unsigned)nstages), round = (int)(stages_done / (unsigned)nstages);
+            bool aborted = false;
             seq_consume_item<WPG, BIAS>(slot, round, aborted, n_begin, n_end, k0, G.q, G.g, G.K, N, op.partial, op.q_bias, p.a_rows, p.status);
+            stages_done += (unsigned)(((n_end - n_begin + kStageCols - 1) / kStageCols) * G.q);
 
             // split-k finish: the last CTA of the column tile publishes it
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
@@ -455,10 +456,8 @@ gemv_seq_kernel(const __grid_constant__ SeqParams p) {
                 const unsigned prev = atomicAdd(op.counters + tile, 1u);
                 *s_flag = (prev == (unsigned)nslabs - 1u);
                 if (prev == (unsigned)nslabs - 1u) op.counters[tile] = 0u;
-                if (tr && getenv_dbg) tr[0] = global_ns();
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kConsWarps * 32) : "memory");
-            if (tr && getenv_dbg) tr[1] = global_ns();
             if (*s_flag) {
                 __threadfence();
                 seq_publish(op, n_begin, n_end, seq, tid);

@@ -122,18 +122,32 @@ def test_first_batched_call_inside_a_stream_capture():
     w.close(); w2.close()
 
 
-def test_host_buffer_call_replays_its_graph_and_profiles():
+def test_host_buffer_call_on_pinned_and_on_pageable_buffers():
+    """Page-locked buffers: a fetch kernel, the matvec storing into the host buffer, a completion word the host polls (no
+    copy engine, no stream synchronisation).  Pageable buffers: copy-in / kernels / copy-out.  Either way the call is
+    replayed as one graph from the second call with the same buffers on."""
     N, K, q, g = 2048, 1024, 3, 128
     bW, a16, _, w = _layer(N, K, q, g, seed=61)
     lib = capi.lib()
     xin = torch.empty((1, K), dtype=torch.int16).pin_memory()
     yout = torch.empty((1, N), dtype=torch.int16).pin_memory()
-    for rep in range(4):                                      # call 0: direct; 1..: the recorded graph, new data each time
+    n0 = lib.lutgemm_kernel_launch_count()
+    for rep in range(4):                                      # new data in the same buffers each time
         x = synth.activations(1, K, seed=100 + rep)
         xin.numpy()[:] = x.view(np.int16)
+        yout.zero_()
         capi.check(lib.lutgemm_matmul_host(yout.data_ptr(), xin.data_ptr(), w.handle, 1), "matmul_host")
         ref = oracle.bcq_matmul_fp32(x, bW, a16, None, g)
-        assert_parity(yout.numpy().view(np.float16).astype(np.float32), ref, K, f"call {rep}")
+        assert_parity(yout.numpy().view(np.float16).astype(np.float32), ref, K, f"pinned call {rep}")
+    assert lib.lutgemm_kernel_launch_count() - n0 == 12       # fetch, matvec, completion word per call; no copies
+    xp = np.empty((3, K), np.float16)                         # pageable, three rows
+    yp = np.empty((3, N), np.float16)
+    for rep in range(3):                                      # call 0: direct; 1..: the recorded graph
+        x = synth.activations(3, K, seed=200 + rep)
+        xp[:] = x
+        L.matmul_host(yp, xp, w, 3)
+        ref = oracle.bcq_matmul_fp32(x, bW, a16, None, g)
+        assert_parity(yp.astype(np.float32), ref, K, f"pageable call {rep}")
     us = (C.c_float * 4)()
     capi.check(lib.lutgemm_matmul_host_profile(yout.data_ptr(), xin.data_ptr(), w.handle, 1, us), "matmul_host_profile")
     assert all(v > 0 for v in us) and us[3] >= us[1]
