@@ -267,6 +267,10 @@ int lutgemm_sequence_commit(lutgemm_sequence_t s);
 int lutgemm_sequence_run(lutgemm_sequence_t s, void* stream);
 /* Synchronises with the device and reads the sequence's status word (0 = every wait was met). */
 int lutgemm_sequence_status(lutgemm_sequence_t s, int* status);
+/* Synchronises and sets the status word back to 0.  A failed step leaves the sequence consistent (every CTA still walks
+ * the whole list, counters and reduction rows are left as a good step leaves them), but while the word is set every wait
+ * gives up at once; clear it once the cause (a peer that was late or gone) is dealt with. */
+int lutgemm_sequence_clear_status(lutgemm_sequence_t s);
 /* Time limit of one in-kernel wait for another matvec's or rank's data, in milliseconds (default 2000). */
 int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds);
 /* Tracing: with a device buffer of n_ops * ctas * 4 uint64 (ctas from lutgemm_sequence_describe) every later run

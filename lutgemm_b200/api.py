@@ -390,6 +390,9 @@ class MatvecSequence:
         capi.check(capi.lib().lutgemm_sequence_status(self._h, C.byref(st)), "sequence_status")
         return st.value
 
+    def clear_status(self):
+        capi.check(capi.lib().lutgemm_sequence_clear_status(self._h), "sequence_clear_status")
+
     def set_wait_limit(self, milliseconds):
         capi.check(capi.lib().lutgemm_sequence_set_wait_limit(self._h, int(milliseconds)), "sequence_set_wait_limit")
 

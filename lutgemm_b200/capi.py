@@ -21,7 +21,7 @@ SYMBOLS = (
     "lutgemm_matvec_static_scratch", "lutgemm_static_scratch_status", "lutgemm_dequantize",
     "lutgemm_matvec_tp", "lutgemm_matvec_tiles", "lutgemm_tp_finalize",
     "lutgemm_sequence_create", "lutgemm_sequence_export", "lutgemm_sequence_connect", "lutgemm_sequence_commit",
-    "lutgemm_sequence_run", "lutgemm_sequence_status", "lutgemm_sequence_set_wait_limit", "lutgemm_sequence_set_trace", "lutgemm_sequence_describe",
+    "lutgemm_sequence_run", "lutgemm_sequence_status", "lutgemm_sequence_clear_status", "lutgemm_sequence_set_wait_limit", "lutgemm_sequence_set_trace", "lutgemm_sequence_describe",
     "lutgemm_sequence_destroy",
     "lutgemm_ipc_alloc", "lutgemm_ipc_open", "lutgemm_ipc_close", "lutgemm_ipc_free",
     "lutgemm_pack_planes", "lutgemm_pack_planes_device", "lutgemm_uniform_to_bcq", "lutgemm_uniform_to_bcq_device",
@@ -111,6 +111,7 @@ def lib():
     L.lutgemm_sequence_commit.argtypes = [vp]
     L.lutgemm_sequence_run.argtypes = [vp, vp]
     L.lutgemm_sequence_status.argtypes = [vp, C.POINTER(ip)]
+    L.lutgemm_sequence_clear_status.argtypes = [vp]
     L.lutgemm_sequence_set_wait_limit.argtypes = [vp, ip]
     L.lutgemm_sequence_set_trace.argtypes = [vp, vp, C.c_size_t]
     L.lutgemm_sequence_describe.argtypes = [vp, C.POINTER(ip), C.POINTER(ip), C.POINTER(C.c_size_t)]

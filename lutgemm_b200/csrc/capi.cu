@@ -1323,6 +1323,13 @@ int lutgemm_sequence_status(lutgemm_sequence_t s, int* status) {
     return LUTGEMM_OK;
 }
 
+int lutgemm_sequence_clear_status(lutgemm_sequence_t s) {
+    if (!s) return LUTGEMM_ERR_NULL;
+    LG_CUDA(cudaDeviceSynchronize());
+    LG_CUDA(cudaMemset(s->words + 2, 0, sizeof(int)));
+    return LUTGEMM_OK;
+}
+
 int lutgemm_sequence_set_wait_limit(lutgemm_sequence_t s, int milliseconds) {
     if (!s) return LUTGEMM_ERR_NULL;
     if (milliseconds < 1 || milliseconds > 60000) return LUTGEMM_ERR_SHAPE;

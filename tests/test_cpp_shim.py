@@ -41,7 +41,8 @@ def test_reference_style_program_runs():
 
 
 # ---- the reference's own benchmark translation unit, unmodified, against this library ----
-REF = os.environ.get("LUTGEMM_REFERENCE", "/root/reference")
+from oracle import oracle as _oracle  # noqa: E402  (the one place that knows where the reference tree lies: oracle/Makefile)
+REF = os.environ.get("LUTGEMM_REFERENCE") or _oracle._makefile_default_ref()
 REF_TU = os.path.join(REF, "tests", "opt", "fp16", "int3_col_wise_matmul_fp16.cu")
 REF_EXE = os.path.join(ROOT, "oracle", "_ref", "ref_layer175b_test")
 

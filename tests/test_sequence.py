@@ -114,6 +114,8 @@ def test_a_wait_that_nothing_satisfies_runs_out_and_is_reported():
     seq.run()
     torch.cuda.synchronize()                                            # returns: the wait is bounded
     assert seq.status() & 4
+    seq.clear_status()
+    assert seq.status() == 0
     seq.close()
     xh = synth.activations(1, K, seed=1)
     L.matmul(y, _dev16(xh), w, 1)
