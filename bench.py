@@ -579,19 +579,19 @@ def run_gptq(a):
 
 
 def batched_numbers(local):
-    """Config 4's batched corner on this GPU: n = k = 8192, q = 2, g = 64 at m = 16 and m = 128 through lutgemm_matmul (the
-    tcgen05 kernel), CUDA-graph replay over 8 weight sets, with the reference's own batched path (dequantise + cuBLAS,
-    child process) beside it.  Returns the dict for the bench line's "batched" key."""
+    """Config 4's batched corner on this GPU: n = k = 8192, q = 2, g = 64 at m = 2 (the two-row LUT kernel), m = 16 and
+    m = 128 (the tcgen05 kernel) through lutgemm_matmul, CUDA-graph replay over 8 weight sets, with the reference's own
+    batched path (dequantise + cuBLAS, child process) beside it.  Returns the dict for the bench line's "batched" key."""
     import torch
     import lutgemm_b200 as L
     n = k = 8192
     q, g, rot = 2, 64, 8
-    out = {"workload": f"bcq_gemm n={n} k={k} q={q} g={g}", "kernel": "gemm_tc_kernel"}
+    out = {"workload": f"bcq_gemm n={n} k={k} q={q} g={g}", "kernels": {"m2": "gemv_tma2_kernel", "m16": "gemm_tc_kernel", "m128": "gemm_tc_kernel"}}
     ws = []
     for i in range(rot):
         bW, alpha, _ = synth.bcq_layer(n, k, q, g, seed=synth.seed_for("bench", n, k, q, i))
         ws.append(L.nQWeight_fp16(bW, alpha, k, n, q, False, k // g).reserve_batch(128))
-    for m in (16, 128):
+    for m in (2, 16, 128):
         xh = synth.activations(m, k, seed=77)
         x = torch.from_numpy(xh.view(np.int16)).cuda().view(torch.float16)
         y = torch.empty((m, n), dtype=torch.float16, device="cuda")

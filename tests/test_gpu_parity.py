@@ -64,11 +64,16 @@ def oracle_y_dense16(bW, alpha, q_bias, g, x):
     return oracle.bcq_matmul_ref(x, bW, alpha.astype(np.float16), None if q_bias is None else q_bias.astype(np.float16), g)
 
 
-def check(y, ref, K, what, fp32_out=False):
+def check(y, ref, K, what, fp32_out=False, wide_range=False):
+    """The matvec tolerance.  wide_range: shapes outside the configurations' (q, K) range, drawn with the configurations'
+    alpha distribution, whose outputs can be several units large: there an exact result rounded to fp16 already has a
+    mean absolute error of about 2^-12 of the mean magnitude, which is added to the bound for the fp16 output (the fp32
+    output is held to the plain bound everywhere)."""
     rel, mae = error_metrics(y, ref)
     assert rel <= MAX_REL, f"{what}: max rel err {rel:.3e}"
     if fp32_out or K <= 12288:
-        assert mae <= MAE, f"{what}: MAE {mae:.3e}"
+        bound = MAE if (fp32_out or not wide_range) else MAE + float(np.abs(ref).mean()) * 2.0 ** -12
+        assert mae <= bound, f"{what}: MAE {mae:.3e} > {bound:.3e}"
     return rel, mae
 
 
@@ -336,15 +341,14 @@ def test_random_configurations(seed):
     fallback, tensor-core batched kernel with either operand order) must agree with the fp32 host reference."""
     rng = np.random.default_rng(1000 + seed)
     N, K, q, g, m, bias = _random_config(rng)
-    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=seed, with_bias=bias, signed_alpha=bool(seed & 1),
-                                    alpha_std=min(0.02, 0.6 / np.sqrt(K * q)))
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=seed, with_bias=bias, signed_alpha=bool(seed & 1))   # alpha ~ |N(0, 0.02)|
     x = synth.activations(m, K, seed=seed + 7)
     ref = oracle_y(bW, alpha, qb, g, x)
     y32 = run_matmul(bW, alpha, qb, g, x, f32=True)
     y16 = run_matmul(bW, alpha, qb, g, x)
     what = f"N={N} K={K} q={q} g={g} m={m} bias={bias}"
     check(y32, ref, K, what + " fp32 out", fp32_out=True)
-    check(y16.astype(np.float32), ref, K, what)
+    check(y16.astype(np.float32), ref, K, what, wide_range=True)
 
 
 @pytest.mark.parametrize("N,K,q,g,m,bias", [(2048, 4096, 3, 128, 2, False), (1032, 1184, 4, 32, 3, True), (512, 512, 1, 512, 2, True),
@@ -352,8 +356,7 @@ def test_random_configurations(seed):
 def test_two_row_matvec_matches_single_rows(N, K, q, g, m, bias):
     """m = 2, 3 through the two-table kernel (weights read once for two rows) against the fp32 host reference and against
     one launch per row."""
-    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=N + K + m, with_bias=bias, signed_alpha=True,
-                                    alpha_std=min(0.02, 0.6 / np.sqrt(K * q)))
+    bW, alpha, qb = synth.bcq_layer(N, K, q, g, seed=N + K + m, with_bias=bias, signed_alpha=True)
     x = synth.activations(m, K, seed=m + 40)
     ref = oracle_y(bW, alpha, qb, g, x)
     lib = capi.lib()
@@ -367,6 +370,6 @@ def test_two_row_matvec_matches_single_rows(N, K, q, g, m, bias):
         lib.lutgemm_set_row_pairs(1)
         lib.lutgemm_set_batched_path(1)
     check(y_pair, ref, K, "two-row kernel, fp32 out", fp32_out=True)
-    check(y_pair16.astype(np.float32), ref, K, "two-row kernel")
+    check(y_pair16.astype(np.float32), ref, K, "two-row kernel", wide_range=True)
     rms = np.sqrt((ref ** 2).mean())
     assert np.abs(y_pair - y_single).max() <= 1e-5 * max(rms, 1e-6) * np.sqrt(K / 512)      # same sums, reduction order aside
