@@ -76,6 +76,7 @@ def parse():
     ap.add_argument("--ntile", type=int, default=0, help="columns per CTA of the matvec (0 = automatic)")
     ap.add_argument("--variant", type=int, default=0, help="0 = bulk-copy fed matvec kernel, 1 = register-streaming kernel")
     ap.add_argument("--ordered", action="store_true", help="bit-reproducible split-k (slabs added in order)")
+    ap.add_argument("--int8", action="store_true", help="batches of up to 16 rows: the integer tensor-core kernel instead of the fp16 one")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -661,6 +662,7 @@ def run_ours(a):
         lib.lutgemm_set_gemv_ntile(a.ntile)
     lib.lutgemm_set_gemv_variant(a.variant)
     lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
+    lib.lutgemm_set_batched_int8(1 if a.int8 else 0)
     lib.lutgemm_set_ordered_reduction(1 if a.ordered else 0)
     kernel_name = (("gemv_tma_kernel" if a.m == 1 else "gemv_tma2_kernel") if a.variant == 0 else "gemv_reg_kernel") if a.m < 4 else "gemm_tc_kernel"
 

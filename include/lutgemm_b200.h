@@ -384,6 +384,14 @@ int lutgemm_set_row_pairs(int enabled);
  * matvec per row; 0: always one LUT matvec per row; 2: tensor-core kernel from m = 2.  All compute the same
  * function. */
 int lutgemm_set_batched_path(int mode);
+/* 0 (default): every batch on the tensor-core path takes the fp16 kernel (operand = +-alpha in fp16, exact products).
+ * 1: a batch of up to 16 rows on a container of up to 4 planes runs the integer kernel (tcgen05.mma.kind::i8): the packed
+ * bits are the operand as they are, the activations are taken as block-scaled 24-bit integers per 128 k and row (every
+ * fp16 input within 2^13 of its block's maximum exactly, the rest to 2^-24 of that maximum; a block with a non-finite
+ * input yields NaN for its row), the scales are applied in fp32 to exact int32 sums.  Same results to fp32 rounding;
+ * measured slower than the fp16 kernel on B200 (one accumulator hand-over per scale group and plane), kept as an
+ * alternative. */
+int lutgemm_set_batched_int8(int enabled);
 /* Tuning knob: 1 (default) launches the TMA-fed matvec with programmatic stream serialization, so
  * that its weight stream starts while the previous kernel of the stream drains; 0 = plain launches. */
 int lutgemm_set_dependent_launch(int enabled);

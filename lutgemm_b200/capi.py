@@ -29,7 +29,7 @@ SYMBOLS = (
     "lutgemm_packer_pack_device", "lutgemm_packer_unpack_device", "lutgemm_from_python_layout_device",
     "lutgemm_bcq_quantize", "lutgemm_bcq_quantize_device", "lutgemm_matmul_gptq",
     "lutgemm_status_string", "lutgemm_last_cuda_error", "lutgemm_kernel_launch_count", "lutgemm_set_gemv_ntile",
-    "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_ordered_reduction", "lutgemm_set_row_pairs", "lutgemm_weight_device_status",
+    "lutgemm_set_gemv_variant", "lutgemm_set_dependent_launch", "lutgemm_set_batched_path", "lutgemm_set_batched_int8", "lutgemm_set_ordered_reduction", "lutgemm_set_row_pairs", "lutgemm_weight_device_status",
 )
 
 
@@ -138,6 +138,7 @@ def lib():
     L.lutgemm_set_gemv_variant.argtypes = [ip]
     L.lutgemm_set_dependent_launch.argtypes = [ip]
     L.lutgemm_set_batched_path.argtypes = [ip]
+    L.lutgemm_set_batched_int8.argtypes = [ip]
     L.lutgemm_set_ordered_reduction.argtypes = [ip]
     L.lutgemm_set_row_pairs.argtypes = [ip]
     L.lutgemm_weight_device_status.argtypes = [vp, C.POINTER(ip)]

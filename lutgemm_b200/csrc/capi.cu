@@ -19,6 +19,7 @@
 #include "gemv_tma2.cuh"
 #include "gemv_seq.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_i8.cuh"
 #include "bcq_quantize.cuh"
 #include "gptq3.cuh"
 
@@ -105,6 +106,7 @@ std::atomic<int> g_pdl{1};
 std::atomic<int> g_ordered{0};
 std::atomic<int> g_pairs{1};     // 1: rows that go through the LUT matvec are taken two at a time where possible
 std::atomic<int> g_batched{1};   // 0: one matvec per row; 1: tensor-core kernel from kBatchedFromRows rows; 2: from 2 rows
+std::atomic<int> g_int8{0};      // 1: batches of up to 16 rows take the integer tensor-core kernel (measured slower: off)
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
@@ -484,6 +486,43 @@ int launch_gemm_tc_q(const lutgemm_weight* w, const CUtensorMap& tmX, const lg::
     return LUTGEMM_OK;
 }
 
+// Split-k plan of a batched launch (256-column tiles x k-ranges of whole 128-k steps) and, when it splits, the fp32
+// reduction rows of the workspace.
+int tc_split(lutgemm_weight* w, lutgemm_workspace* ws, int m, cudaStream_t st, int* splitk_out, int* steps_per_cta_out) {
+    const int tiles = (w->N + lg::kTcTileN - 1) / lg::kTcTileN;
+    const int steps_total = (w->K + lg::kTcStepK - 1) / lg::kTcStepK;
+    // split-k factor: fill whole waves of one CTA per SM; among equally full choices take the smallest
+    const int sms = sm_count();
+    int splitk = 1, steps_per_cta = 0;
+    double best = 0.0;
+    for (int c = 1; c <= 8 && c <= steps_total; c++) {
+        const int ctas = tiles * c;
+        const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
+        if (eff > best + 0.02) { best = eff; splitk = c; }
+    }
+    if (g_ordered.load()) splitk = 1;             // bit-reproducible mode: no unordered reductions across k-ranges
+    steps_per_cta = (steps_total + splitk - 1) / splitk;
+    splitk = (steps_total + steps_per_cta - 1) / steps_per_cta;
+    if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
+    if (splitk > 1 && ws->tc_rows < m) {
+        // Not reserved (lutgemm_weight_reserve_batch / lutgemm_workspace_create): only the container's own workspace
+        // grows by itself, which synchronises the device and cannot happen inside a stream capture.
+        if (ws != &w->own) return LUTGEMM_ERR_TOO_LARGE;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return LUTGEMM_ERR_BATCH;
+        if (ws->tc_partial) LG_CUDA(cudaFree(ws->tc_partial));
+        ws->tc_partial = nullptr;
+        ws->tc_rows = 0;
+        const int rows = tc_rows_for(m);
+        LG_CUDA(cudaMalloc(&ws->tc_partial, (size_t)rows * w->N * sizeof(float)));
+        LG_CUDA(cudaMemset(ws->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
+        ws->tc_rows = rows;
+    }
+    *splitk_out = splitk;
+    *steps_per_cta_out = steps_per_cta;
+    return LUTGEMM_OK;
+}
+
 // Batched rows [0, m), m in 2..128, through the tensor-core kernel (container must have tc_ok).
 int gemm_tc_rows(lutgemm_weight* w, lutgemm_workspace* ws, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -503,35 +542,12 @@ int gemm_tc_rows(lutgemm_weight* w, lutgemm_workspace* ws, const __half* x, __ha
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return LUTGEMM_ERR_CUDA;
     }
-    const int tiles = (w->N + lg::kTcTileN - 1) / lg::kTcTileN;
-    const int steps_total = (w->K + lg::kTcStepK - 1) / lg::kTcStepK;
-    // split-k factor: fill whole waves of one CTA per SM; among equally full choices take the smallest
-    const int sms = sm_count();
     int splitk = 1;
-    double best = 0.0;
-    for (int c = 1; c <= 8 && c <= steps_total; c++) {
-        const int ctas = tiles * c;
-        const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
-        if (eff > best + 0.02) { best = eff; splitk = c; }
+    {
+        int rc = tc_split(w, ws, m, st, &splitk, &p.steps_per_cta);
+        if (rc != LUTGEMM_OK) return rc;
     }
-    if (g_ordered.load()) splitk = 1;             // bit-reproducible mode: no unordered reductions across k-ranges
-    p.steps_per_cta = (steps_total + splitk - 1) / splitk;
-    splitk = (steps_total + p.steps_per_cta - 1) / p.steps_per_cta;
-    if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
-    if (splitk > 1 && ws->tc_rows < m) {
-        // Not reserved (lutgemm_weight_reserve_batch / lutgemm_workspace_create): only the container's own workspace
-        // grows by itself, which synchronises the device and cannot happen inside a stream capture.
-        if (ws != &w->own) return LUTGEMM_ERR_TOO_LARGE;
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) return LUTGEMM_ERR_BATCH;
-        if (ws->tc_partial) LG_CUDA(cudaFree(ws->tc_partial));
-        ws->tc_partial = nullptr;
-        ws->tc_rows = 0;
-        const int rows = tc_rows_for(m);
-        LG_CUDA(cudaMalloc(&ws->tc_partial, (size_t)rows * w->N * sizeof(float)));
-        LG_CUDA(cudaMemset(ws->tc_partial, 0, (size_t)rows * w->N * sizeof(float)));
-        ws->tc_rows = rows;
-    }
+    const int tiles = (w->N + lg::kTcTileN - 1) / lg::kTcTileN;
     p.partial = ws->tc_partial; p.counters = ws->counters; p.status = ws->status;
     p.y16 = y16; p.y32 = y32;
     p.N = w->N; p.K = w->K; p.g = w->g;
@@ -545,6 +561,74 @@ int gemm_tc_rows(lutgemm_weight* w, lutgemm_workspace* ws, const __half* x, __ha
         case 6: return launch_gemm_tc_q<6>(w, tmX, p, grid, st);
         case 7: return launch_gemm_tc_q<7>(w, tmX, p, grid, st);
         case 8: return launch_gemm_tc_q<8>(w, tmX, p, grid, st);
+    }
+    return LUTGEMM_ERR_BITS;
+}
+
+template <int Q>
+int launch_gemm_i8_q(const lutgemm_weight* w, const CUtensorMap& tmX, const lg::I8Params& p, dim3 grid, cudaStream_t st) {
+    static bool configured[64][2] = {};   // the attribute is per device
+    const bool bias = w->q_bias != nullptr;
+    auto kern = bias ? lg::gemm_i8_kernel<Q, true> : lg::gemm_i8_kernel<Q, false>;
+    int dev = 0;
+    LG_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev][bias]) {
+        LG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lg::kTcSmemTotal));
+        if (dev < 64) configured[dev][bias] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(lg::kI8Threads);
+    cfg.dynamicSmemBytes = (size_t)lg::kTcSmemTotal;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    LG_CUDA(cudaLaunchKernelEx(&cfg, kern, tmX, w->tmWtc, w->tmAtc, w->tmQtc, p));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    LG_CUDA(cudaGetLastError());
+    return LUTGEMM_OK;
+}
+
+// True when a batch of m rows on this container can take the integer tensor-core kernel.
+bool gemm_i8_ok(const lutgemm_weight* w, int m) {
+    if (!w->tc_ok || m < 2 || m > lg::kI8Rows || w->q > 4 || !g_int8.load()) return false;
+    lg::I8Params p = {};
+    return lg::i8_plan(w->q, w->q_bias != nullptr, w->g, p);
+}
+
+// Batched rows [0, m), m in 2..16, through the integer tensor-core kernel (gemm_i8_ok holds).
+int gemm_i8_rows(lutgemm_weight* w, lutgemm_workspace* ws, const __half* x, __half* y16, float* y32, int m, cudaStream_t st) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc || !w->tc_ok) return LUTGEMM_ERR_CUDA;
+    lg::I8Params p = {};
+    if (!lg::i8_plan(w->q, w->q_bias != nullptr, w->g, p)) return LUTGEMM_ERR_TOO_LARGE;
+    p.m = m;
+    CUtensorMap tmX;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)w->K, (cuuint64_t)m};
+        cuuint64_t strides[1] = {(cuuint64_t)w->K * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)lg::kI8Rows};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return LUTGEMM_ERR_CUDA;
+    }
+    int splitk = 1;
+    int rc = tc_split(w, ws, m, st, &splitk, &p.steps_per_cta);
+    if (rc != LUTGEMM_OK) return rc;
+    p.partial = ws->tc_partial; p.counters = ws->counters; p.status = ws->status;
+    p.y16 = y16; p.y32 = y32;
+    p.N = w->N; p.K = w->K; p.g = w->g;
+    dim3 grid((w->N + lg::kTcTileN - 1) / lg::kTcTileN, splitk);
+    switch (w->q) {
+        case 1: return launch_gemm_i8_q<1>(w, tmX, p, grid, st);
+        case 2: return launch_gemm_i8_q<2>(w, tmX, p, grid, st);
+        case 3: return launch_gemm_i8_q<3>(w, tmX, p, grid, st);
+        case 4: return launch_gemm_i8_q<4>(w, tmX, p, grid, st);
     }
     return LUTGEMM_ERR_BITS;
 }
@@ -603,8 +687,10 @@ int matmul_impl(__half* y16, float* y32, const void* in, lutgemm_weight_t w, int
     // batched: 128 rows per tensor-core launch
     for (int r0 = 0; r0 < m; r0 += 128) {
         const int rows = (m - r0 < 128) ? (m - r0) : 128;
-        int rc = gemm_tc_rows(w, ws, x + (size_t)r0 * w->K, y16 ? y16 + (size_t)r0 * w->N : nullptr,
-                              y32 ? y32 + (size_t)r0 * w->N : nullptr, rows, st);
+        const __half* xr = x + (size_t)r0 * w->K;
+        __half* y16r = y16 ? y16 + (size_t)r0 * w->N : nullptr;
+        float* y32r = y32 ? y32 + (size_t)r0 * w->N : nullptr;
+        int rc = gemm_i8_ok(w, rows) ? gemm_i8_rows(w, ws, xr, y16r, y32r, rows, st) : gemm_tc_rows(w, ws, xr, y16r, y32r, rows, st);
         if (rc != LUTGEMM_OK) return rc;
     }
     return LUTGEMM_OK;
@@ -1672,6 +1758,11 @@ int lutgemm_set_row_pairs(int enabled) {
 int lutgemm_set_batched_path(int mode) {
     if (mode < 0 || mode > 2) return LUTGEMM_ERR_SHAPE;
     g_batched.store(mode);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_set_batched_int8(int enabled) {
+    g_int8.store(enabled ? 1 : 0);
     return LUTGEMM_OK;
 }
 

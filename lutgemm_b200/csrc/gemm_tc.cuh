@@ -179,6 +179,84 @@ __device__ __forceinline__ uint32_t umma_idesc_f16_f32(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// One 16-row x 32-column accumulator block of a warp (lane = output column, v[j] = activation row row0 + j), turned through
+// a per-warp scratch of 16 x 33 floats (rows padded: no bank conflicts either way) so that a lane holds 4 consecutive
+// columns of one row: vector reductions / 128-bit stores, a quarter of the L2 transactions of scalar ones.
+// N % 8 == 0 on this path: whole groups of four columns.
+__device__ __forceinline__ void tc_store_block(float* scratch, const uint32_t (&v16)[16], int lane, int row0, int ncol0, int m,
+                                               int N, bool split, float* partial, __half* y16, float* y32) {
+#pragma unroll
+    for (int jj = 0; jj < 16; jj++) scratch[jj * 33 + lane] = __uint_as_float(v16[jj]);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int row = (lane >> 3) + 4 * i, col4 = (lane & 7) * 4;
+        const float* src = scratch + row * 33 + col4;
+        const float4 v = make_float4(src[0], src[1], src[2], src[3]);
+        const int mrow = row0 + row, n = ncol0 + col4;
+        if (mrow < m && n < N) {
+            const size_t o = (size_t)mrow * (size_t)N + n;
+            if (split) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(partial + o), "f"(v.x), "f"(v.y),
+                             "f"(v.z), "f"(v.w) : "memory");
+            } else {
+                if (y32) *reinterpret_cast<float4*>(y32 + o) = v;
+                if (y16) {
+                    __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                    uint2 h2;
+                    h2.x = *reinterpret_cast<uint32_t*>(&lo);
+                    h2.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(y16 + o) = h2;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// Split-k finish, called by every thread of the CTA after its reductions (and a __threadfence + __syncthreads): the last
+// CTA of this column tile converts the reduced sums and zeroes the workspace.
+__device__ __forceinline__ void tc_splitk_finish(float* partial, unsigned* counters, __half* y16, float* y32, int m, int N,
+                                                 int n0, int* s_flag, int nthreads) {
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(counters + blockIdx.x, 1u);
+        *s_flag = (prev == gridDim.y - 1u);
+    }
+    __syncthreads();
+    if (!*s_flag) return;
+    __threadfence();
+    // whole float4 groups, several loads in flight per thread
+    const int nvec = m * (kTcTileN / 4);
+    for (int base = tid; base < nvec; base += 4 * nthreads) {
+        float4 v[4];
+        size_t off[4];
+        bool live[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int idx = base + u * nthreads;
+            const int mrow = idx / (kTcTileN / 4), n = n0 + 4 * (idx % (kTcTileN / 4));
+            live[u] = idx < nvec && n < N;
+            off[u] = (size_t)mrow * (size_t)N + n;
+            if (live[u]) v[u] = __ldcg(reinterpret_cast<const float4*>(partial + off[u]));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (!live[u]) continue;
+            __stcg(reinterpret_cast<float4*>(partial + off[u]), make_float4(0.f, 0.f, 0.f, 0.f));
+            if (y32) *reinterpret_cast<float4*>(y32 + off[u]) = v[u];
+            if (y16) {
+                __half2 lo = __floats2half2_rn(v[u].x, v[u].y), hi = __floats2half2_rn(v[u].z, v[u].w);
+                uint2 o;
+                o.x = *reinterpret_cast<uint32_t*>(&lo);
+                o.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(y16 + off[u]) = o;
+            }
+        }
+    }
+    if (tid == 0) counters[blockIdx.x] = 0u;
+}
+
 // Q: number of bit planes; BIAS: container has q_bias.
 //  tmX: 2-D map {K, m} of fp16, box {64, m_pad}, 128-byte swizzle;
 //  tmW: 3-D map {N, q, K/32} of uint32, box {256, q, 4};  tmA: 3-D map {N, q, G} of fp16, box {256, q, a_rows};
@@ -211,7 +289,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const int step_begin = blockIdx.y * p.steps_per_cta;
     const int nsteps = max(0, min(steps_total, step_begin + p.steps_per_cta) - step_begin);
     constexpr int P = Q + (BIAS ? 1 : 0);                  // q_bias rides as one more plane
-    const size_t rowN = (size_t)N;
     const int m_pad = L.m_pad;
 
     if (tid == 0) {
@@ -459,33 +536,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             uint32_t r[16];
             tmem_ld_x16(t_src + 16u * (uint32_t)c, r);
             tmem_ld_wait();
-#pragma unroll
-            for (int jj = 0; jj < 16; jj++) scratch[jj * 33 + lane] = __uint_as_float(r[jj]);
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int row = (lane >> 3) + 4 * i, col4 = (lane & 7) * 4;
-                const float* src = scratch + row * 33 + col4;
-                const float4 v = make_float4(src[0], src[1], src[2], src[3]);
-                const int mrow = 16 * c + row, n = ncol0 + col4;
-                if (mrow < p.m && n < N) {                 // N % 8 == 0 on this path: whole groups of four columns
-                    const size_t o = (size_t)mrow * rowN + n;
-                    if (split) {
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + o), "f"(v.x), "f"(v.y),
-                                     "f"(v.z), "f"(v.w) : "memory");
-                    } else {
-                        if (p.y32) *reinterpret_cast<float4*>(p.y32 + o) = v;
-                        if (p.y16) {
-                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-                            uint2 h2;
-                            h2.x = *reinterpret_cast<uint32_t*>(&lo);
-                            h2.y = *reinterpret_cast<uint32_t*>(&hi);
-                            *reinterpret_cast<uint2*>(p.y16 + o) = h2;
-                        }
-                    }
-                }
-            }
-            __syncwarp();
+            tc_store_block(scratch, r, lane, 16 * c, ncol0, p.m, N, split, p.partial, p.y16, p.y32);
         }
         tc_fence_before_sync();
     }
@@ -497,43 +548,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
     if (!split) return;
 
-    // split-k finish: the last CTA of this column tile converts the reduced sums and zeroes the workspace
-    if (tid == 0) {
-        const unsigned prev = atomicAdd(p.counters + blockIdx.x, 1u);
-        *s_flag = (prev == gridDim.y - 1u);
-    }
-    __syncthreads();
-    if (!*s_flag) return;
-    __threadfence();
-    // N % 8 == 0 on this path: whole float4 groups, several loads in flight per thread
-    const int nvec = p.m * (kTcTileN / 4);
-    for (int base = tid; base < nvec; base += 4 * kTcThreads) {
-        float4 v[4];
-        size_t off[4];
-        bool live[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int idx = base + u * kTcThreads;
-            const int mrow = idx / (kTcTileN / 4), n = n0 + 4 * (idx % (kTcTileN / 4));
-            live[u] = idx < nvec && n < N;
-            off[u] = (size_t)mrow * rowN + n;
-            if (live[u]) v[u] = __ldcg(reinterpret_cast<const float4*>(p.partial + off[u]));
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            if (!live[u]) continue;
-            __stcg(reinterpret_cast<float4*>(p.partial + off[u]), make_float4(0.f, 0.f, 0.f, 0.f));
-            if (p.y32) *reinterpret_cast<float4*>(p.y32 + off[u]) = v[u];
-            if (p.y16) {
-                __half2 lo = __floats2half2_rn(v[u].x, v[u].y), hi = __floats2half2_rn(v[u].z, v[u].w);
-                uint2 o;
-                o.x = *reinterpret_cast<uint32_t*>(&lo);
-                o.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(p.y16 + off[u]) = o;
-            }
-        }
-    }
-    if (tid == 0) p.counters[blockIdx.x] = 0u;
+    tc_splitk_finish(p.partial, p.counters, p.y16, p.y32, p.m, N, n0, s_flag, kTcThreads);
 }
 
 }  // namespace lg
