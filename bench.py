@@ -664,7 +664,7 @@ def run_ours(a):
     lib.lutgemm_set_dependent_launch(0 if a.no_pdl else 1)
     lib.lutgemm_set_batched_int8(1 if a.int8 else 0)
     lib.lutgemm_set_ordered_reduction(1 if a.ordered else 0)
-    kernel_name = (("gemv_tma_kernel" if a.m == 1 else "gemv_tma2_kernel") if a.variant == 0 else "gemv_reg_kernel") if a.m < 4 else "gemm_tc_kernel"
+    kernel_name = (("gemv_tma_kernel" if a.m == 1 else "gemv_tma2_kernel") if a.variant == 0 else "gemv_reg_kernel") if a.m < 4 else ("gemm_i8_kernel" if a.int8 and a.m <= 16 and a.q <= 4 else "gemm_tc_kernel")
 
     B = synth.algorithmic_bytes(a.n, a.k, a.q, a.g, a.m, a.bias)
     rot = max(1, a.rot)
