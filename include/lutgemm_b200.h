@@ -121,6 +121,11 @@ typedef struct lutgemm_workspace* lutgemm_workspace_t;
 int lutgemm_workspace_create(lutgemm_workspace_t* out, int max_n, int max_k, int max_m);
 int lutgemm_workspace_destroy(lutgemm_workspace_t ws);
 int lutgemm_workspace_status(lutgemm_workspace_t ws, int* status);
+/* Split-k mode of the calls made on this workspace / on the container's own workspace: 0 = unordered fp32 reductions,
+ * 1 = bit-reproducible (see lutgemm_set_ordered_reduction), -1 (initial) = whatever the process-wide setting is when the
+ * call is made.  Each call reads the mode once; a workspace may change mode between calls. */
+int lutgemm_workspace_set_ordered(lutgemm_workspace_t ws, int mode);
+int lutgemm_weight_set_ordered(lutgemm_weight_t w, int mode);
 int lutgemm_matmul_ws(void* out_fp16, const void* in_fp16, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream);
 int lutgemm_matmul_f32_ws(float* out_f32, const void* in_fp16, lutgemm_weight_t w, int m, lutgemm_workspace_t ws, void* stream);
 

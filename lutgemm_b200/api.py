@@ -99,6 +99,11 @@ class nQWeight_fp16:
         capi.check(capi.lib().lutgemm_weight_reserve_batch(self.handle, int(m)), "reserve_batch")
         return self
 
+    def set_ordered(self, mode):
+        """Split-k mode of calls on this container's own workspace: 0, 1, or -1 = the process-wide setting."""
+        capi.check(capi.lib().lutgemm_weight_set_ordered(self.handle, int(mode)), "weight_set_ordered")
+        return self
+
     def getDequantiedWeight(self, onGPU=True):
         """Dense fp16 weight as a torch CUDA tensor: [K, N] column-wise, [N, K] row-wise
         (lutGEMM/src/nQWeight_fp16.cu:93-99).  Only the GPU path exists here."""
@@ -139,6 +144,11 @@ class Workspace:
         st = C.c_int(-1)
         capi.check(capi.lib().lutgemm_workspace_status(self._h, C.byref(st)), "workspace_status")
         return st.value
+
+    def set_ordered(self, mode):
+        """0 = unordered reductions, 1 = bit-reproducible, -1 = follow the process-wide setting (the initial state)."""
+        capi.check(capi.lib().lutgemm_workspace_set_ordered(self._h, int(mode)), "workspace_set_ordered")
+        return self
 
     def close(self):
         if self._h:

@@ -16,7 +16,7 @@ ERR_NULL, ERR_SHAPE, ERR_BITS, ERR_BATCH, ERR_CUDA, ERR_NO_DEVICE, ERR_TOO_LARGE
 SYMBOLS = (
     "lutgemm_weight_create", "lutgemm_weight_create_device", "lutgemm_weight_destroy", "lutgemm_weight_describe",
     "lutgemm_matmul", "lutgemm_matmul_f32", "lutgemm_matmul_host", "lutgemm_matmul_host_profile", "lutgemm_matmul_wx",
-    "lutgemm_weight_reserve_batch", "lutgemm_workspace_create", "lutgemm_workspace_destroy", "lutgemm_workspace_status",
+    "lutgemm_weight_reserve_batch", "lutgemm_workspace_create", "lutgemm_workspace_destroy", "lutgemm_workspace_status", "lutgemm_workspace_set_ordered", "lutgemm_weight_set_ordered",
     "lutgemm_matmul_ws", "lutgemm_matmul_f32_ws",
     "lutgemm_matvec_static_scratch", "lutgemm_static_scratch_status", "lutgemm_dequantize",
     "lutgemm_matvec_tp", "lutgemm_matvec_tiles", "lutgemm_tp_finalize",
@@ -94,6 +94,8 @@ def lib():
     L.lutgemm_workspace_create.argtypes = [C.POINTER(vp), ip, ip, ip]
     L.lutgemm_workspace_destroy.argtypes = [vp]
     L.lutgemm_workspace_status.argtypes = [vp, C.POINTER(ip)]
+    L.lutgemm_workspace_set_ordered.argtypes = [vp, ip]
+    L.lutgemm_weight_set_ordered.argtypes = [vp, ip]
     L.lutgemm_matmul_ws.argtypes = [vp, vp, vp, ip, vp, vp]
     L.lutgemm_matmul_f32_ws.argtypes = [vp, vp, vp, ip, vp, vp]
     L.lutgemm_static_scratch_status.argtypes = [C.POINTER(ip)]

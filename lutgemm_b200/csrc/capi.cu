@@ -37,6 +37,7 @@ struct lutgemm_workspace {
     void* t_in = nullptr;
     void* t_out = nullptr;
     size_t t_in_bytes = 0, t_out_bytes = 0;
+    std::atomic<int> ordered{-1};   // split-k mode of calls on this workspace: -1 = the process-wide setting, 0 / 1 = fixed
 };
 
 struct lutgemm_weight {
@@ -108,6 +109,8 @@ std::atomic<int> g_pairs{1};     // 1: rows that go through the LUT matvec are t
 std::atomic<int> g_batched{1};   // 0: one matvec per row; 1: tensor-core kernel from kBatchedFromRows rows; 2: from 2 rows
 std::atomic<int> g_int8{0};      // 1: batches of up to 16 rows take the integer tensor-core kernel (measured slower: off)
 std::atomic<int> g_variant{0};   // 0: bulk-copy fed kernel (default); 1: register-streaming kernel
+// Split-k mode of a call on this workspace (read once per call).
+inline int ordered_for(const lutgemm_workspace* ws);
 constexpr int kMaxCounters = 4096;
 constexpr int kMaxBatch = 65536;
 constexpr int kBatchedFromRows = 4;      // m >= 4 goes to the tensor-core kernel
@@ -228,10 +231,21 @@ void free_workspace_buffers(lutgemm_workspace* ws) {
     if (ws->tc_partial) cudaFree(ws->tc_partial);
     if (ws->t_in) cudaFree(ws->t_in);
     if (ws->t_out) cudaFree(ws->t_out);
-    *ws = lutgemm_workspace();
+    ws->partial = ws->partial2 = ws->tc_partial = nullptr;
+    ws->counters = nullptr;
+    ws->status = nullptr;
+    ws->t_in = ws->t_out = nullptr;
+    ws->tc_rows = ws->n_cap = ws->slabs = 0;
+    ws->t_in_bytes = ws->t_out_bytes = 0;
+    ws->ordered.store(-1);
 }
 
 // Rows of the batched path's fp32 workspace for a batch of m (a multiple of 16, at most 128 per launch).
+inline int ordered_for(const lutgemm_workspace* ws) {
+    const int o = ws ? ws->ordered.load() : -1;
+    return o >= 0 ? o : g_ordered.load();
+}
+
 int tc_rows_for(int m) {
     const int rows = m > 128 ? 128 : m;
     return (rows + 15) / 16 * 16;
@@ -376,7 +390,7 @@ int launch_gemv_tma_any(const lutgemm_weight* w, const lutgemm_workspace* ws, co
     int tiles = 0;
     gemv_tma_geometry(w, &p2.nslabs, &p2.n_tile, &tiles);
     p2.a_rows = w->a_rows;
-    p2.ordered = g_ordered.load();
+    p2.ordered = ordered_for(ws);
     if (link) p2.tp = *link;
     dim3 grid2(tiles, p2.nslabs);
     const bool bias2 = w->q_bias != nullptr;
@@ -430,7 +444,7 @@ int gemv_pair(const lutgemm_weight* w, const lutgemm_workspace* ws, const __half
     return launch_gemv_tma2<1>(w, p, grid, bias, st);
 }
 bool gemv_pair_ok(const lutgemm_weight* w, const lutgemm_workspace* ws) {
-    return g_variant.load() == 0 && w->tma_ok && ws->partial2 && !g_ordered.load() && g_pairs.load() &&
+    return g_variant.load() == 0 && w->tma_ok && ws->partial2 && !ordered_for(ws) && g_pairs.load() &&
            lg::gemv22_num_stages(w->a_rows) >= 2;
 }
 
@@ -446,7 +460,7 @@ int gemv_row(const lutgemm_weight* w, const lutgemm_workspace* ws, const __half*
         p.N = w->N; p.K = w->K; p.q = w->q; p.g = w->g;
         p.nslabs = (w->K + lg::kSlab2 - 1) / lg::kSlab2;
         p.n_tile = choose_ntile(w->N, p.nslabs, 1, lg::kStageCols);
-        p.ordered = g_ordered.load();
+        p.ordered = ordered_for(ws);
         dim3 grid((w->N + p.n_tile - 1) / p.n_tile, p.nslabs);
         const bool bias = w->q_bias != nullptr;
         if (w->g % 128 == 0) return launch_gemv_reg<2>(p, grid, bias, st);
@@ -500,7 +514,7 @@ int tc_split(lutgemm_weight* w, lutgemm_workspace* ws, int m, cudaStream_t st, i
         const double eff = (double)ctas / ((double)((ctas + sms - 1) / sms) * sms);
         if (eff > best + 0.02) { best = eff; splitk = c; }
     }
-    if (g_ordered.load()) splitk = 1;             // bit-reproducible mode: no unordered reductions across k-ranges
+    if (ordered_for(ws)) splitk = 1;             // bit-reproducible mode: no unordered reductions across k-ranges
     steps_per_cta = (steps_total + splitk - 1) / splitk;
     splitk = (steps_total + steps_per_cta - 1) / steps_per_cta;
     if (tiles > kMaxCounters) return LUTGEMM_ERR_TOO_LARGE;
@@ -922,6 +936,18 @@ int lutgemm_workspace_status(lutgemm_workspace_t ws, int* status) {
     if (!ws || !status) return LUTGEMM_ERR_NULL;
     LG_CUDA(cudaMemcpy(status, ws->status, sizeof(int), cudaMemcpyDeviceToHost));
     return LUTGEMM_OK;
+}
+
+int lutgemm_workspace_set_ordered(lutgemm_workspace_t ws, int mode) {
+    if (!ws) return LUTGEMM_ERR_NULL;
+    if (mode < -1 || mode > 1) return LUTGEMM_ERR_SHAPE;
+    ws->ordered.store(mode);
+    return LUTGEMM_OK;
+}
+
+int lutgemm_weight_set_ordered(lutgemm_weight_t w, int mode) {
+    if (!w) return LUTGEMM_ERR_NULL;
+    return lutgemm_workspace_set_ordered(&w->own, mode);
 }
 
 int lutgemm_weight_reserve_batch(lutgemm_weight_t w, int m) {

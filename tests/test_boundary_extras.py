@@ -62,6 +62,39 @@ def test_modes_may_be_switched_on_one_container():
     w.close()
 
 
+def test_ordered_mode_per_workspace_overrides_the_process_setting():
+    """A workspace (or a container's own) fixed to the bit-reproducible mode repeats its result exactly while the
+    process-wide setting stays on the default; -1 hands it back to the process-wide setting."""
+    N, K, q, g = 4096, 12288, 3, 128
+    bW, a16, _, w = _layer(N, K, q, g, seed=33)
+    x = synth.activations(1, K, seed=9)
+    ref = oracle.bcq_matmul_fp32(x, bW, a16, None, g)
+    xd = _dev16(x)
+    ws = L.Workspace(N, K, 1).set_ordered(1)
+    runs = []
+    for _ in range(3):
+        y = torch.zeros((1, N), dtype=torch.float32, device="cuda")
+        L.matmul_f32(y, xd, w, 1, workspace=ws)
+        torch.cuda.synchronize()
+        runs.append(y.cpu().numpy())
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    assert_parity(runs[0], ref, K, "ordered workspace")
+    w.set_ordered(1)
+    y1 = torch.zeros((1, N), dtype=torch.float32, device="cuda")
+    L.matmul_f32(y1, xd, w, 1)
+    torch.cuda.synchronize()
+    assert np.array_equal(y1.cpu().numpy(), runs[0])          # the same slab order on the container's own workspace
+    w.set_ordered(-1)
+    ws.set_ordered(-1)
+    y2 = torch.zeros((1, N), dtype=torch.float32, device="cuda")
+    L.matmul_f32(y2, xd, w, 1, workspace=ws)
+    torch.cuda.synchronize()
+    assert_parity(y2.cpu().numpy(), ref, K, "back on the process-wide setting")
+    assert capi.lib().lutgemm_workspace_set_ordered(ws.handle, 2) == capi.ERR_SHAPE
+    ws.close()
+    w.close()
+
+
 def test_two_streams_share_a_container_through_their_own_workspaces():
     N, K, q, g = 4096, 4096, 3, 128
     bW, a16, _, w = _layer(N, K, q, g, seed=41)

@@ -112,6 +112,12 @@ def test_create_rejects_bad_shapes_before_touching_cuda():
 
 
 @pytest.mark.skipif(_has_gpu(), reason="checks the no-GPU failure mode")
+def test_ordered_setters_reject_null_handles():
+    lib = capi.lib()
+    assert lib.lutgemm_workspace_set_ordered(None, 1) == capi.ERR_NULL
+    assert lib.lutgemm_weight_set_ordered(None, 1) == capi.ERR_NULL
+
+
 def test_compute_fails_loudly_without_gpu():
     bW, alpha, _ = synth.bcq_layer(8, 64, 2, 32, seed=1)
     with pytest.raises(L.LutGemmError) as e:
