@@ -152,14 +152,17 @@ dist.destroy_process_group()
 '''
 
 
-def test_sequence_program_of_the_stack_over_gloo_matches_collectives(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_program_of_the_stack_over_gloo_matches_collectives(tmp_path, world):
     """The list of matvecs and exchange buffers that the one-launch stack hands to lutgemm_sequence_create, executed by a
-    host model of the exchange on two CPU ranks, against the same shards run through gloo all-gather / all-reduce."""
+    host model of the exchange on two and on four CPU ranks, against the same shards run through gloo all-gather /
+    all-reduce."""
     script = tmp_path / "seq_worker.py"
     script.write_text(SEQ_WORKER)
-    env = dict(os.environ, LG_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29617", WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    env = dict(os.environ, LG_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29617 + world), WORLD_SIZE=str(world),
+               OMP_NUM_THREADS="2")
     procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
-                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o
